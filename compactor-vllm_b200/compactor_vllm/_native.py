@@ -94,10 +94,19 @@ _SIGNATURES = {
     "cvllm_gated_group_norm": (_i, [_p, _i64, _p, _i64, _p, _f, _p, _i64, _i64, _i, _i, _i, _p]),
     "cvllm_qknorm_store": (_i, [_p, _i64, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _p,
                                 _i, _i, _i, _i, _i, _i, _i, _p]),
-    "cvllm_bias_attn_varlen": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _f, _p,
+    "cvllm_rope_qknorm_store": (_i, [_p, _i64, _p, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _p,
+                                     _i, _i, _i, _i, _i, _i, _i, _p]),
+    "cvllm_bias_attn_varlen": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _p, _f, _p,
                                     _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i64, _i, _p]),
-    "cvllm_bias_attn_decode": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _i, _i, _f, _p,
+    "cvllm_bias_attn_decode": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _i, _i, _p, _f, _p,
                                     _i, _i, _i, _i, _i, _i, _i, _p, _sz, _i64, _i, _p]),
+    "cvllm_residual_norm": (_i, [_p, _i64, _p, _i64, _i, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i, _i, _i, _f, _i, _p]),
+    "cvllm_pair_hash_embed": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p, _i64, _i, _i, _i, _i, _p]),
+    "cvllm_token_shift_mix": (_i, [_p, _i64, _p, _i, _i, _p, _p, _p, _p, _p, _i, _i, _p, _i64, _i, _i, _p]),
+    "cvllm_delta_rule": (_i, [_p, _i64, _p, _i64, _i, _i, _p, _p, _p, _p, _i64, _i, _p, _i, _f, _p, _p, _p, _p, _i, _i,
+                              _p, _i64, _i, _i, _i, _i, _i, _i, _p]),
+    "cvllm_wkv_scan": (_i, [_p, _i64, _p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _i64, _i, _p, _i, _f, _p, _p, _p, _p,
+                            _i, _i, _p, _i64, _i, _i, _i, _i, _p]),
 }
 
 _lib = None

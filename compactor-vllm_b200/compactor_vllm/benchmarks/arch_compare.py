@@ -196,7 +196,8 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
         c = get_context()
         N.check(lib.cvllm_bias_attn_varlen(N.ptr(q), N.ptr(attn.k_cache), N.ptr(attn.v_cache), *table,
                                            N.ptr(c.cu_seqlens_q), N.ptr(c.seq_start), N.ptr(c.batch_mapping),
-                                           N.ptr(attn.slopes), attn.chunk, 1, attn.scale, N.ptr(out), 1, L, H, G, D, D,
+                                           N.ptr(attn.slopes), attn.chunk, 1, None, attn.scale, N.ptr(out), 1, L, H, G,
+                                           D, D,
                                            L, attn.k_cache.shape[0], pt.shape[-1], 0, code, N.stream(dev)), "varlen")
 
     prefill_ctx(0)
@@ -218,7 +219,8 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
         splits = attn.decode_splits(B, L)
         ws = N.workspace(dev, 4 * B * H * splits * (2 + D), "bias_attn_decode")
         N.check(lib.cvllm_bias_attn_decode(N.ptr(qd), N.ptr(attn.k_cache), N.ptr(attn.v_cache), *table, N.ptr(pos),
-                                           N.ptr(bm), N.ptr(attn.slopes), chunk, 1, attn.scale, N.ptr(od), B, H, G, D, D,
+                                           N.ptr(bm), N.ptr(attn.slopes), chunk, 1, None, attn.scale, N.ptr(od), B, H, G,
+                                           D, D,
                                            0, splits, N.ptr(ws), ws.numel(), 0, code, N.stream(dev)), "decode")
 
     add("bias_attn_decode (no chunk, 8 x 4096)", timed(lambda: decode(0)), nbytes=2 * 2 * B * G * L * D,

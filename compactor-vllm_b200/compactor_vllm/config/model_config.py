@@ -282,7 +282,155 @@ class BatasunConfig:
         return max([l.mixer.kv_rank + l.mixer.rot_dim for l in self.layers if l.mixer_type == "latent_attention"] or [1])
 
 
-ARCHITECTURES = {"Movolorn": MovolornConfig, "Batasun": BatasunConfig}
+@dataclass
+class RotaryAttentionConfig:
+    """Grouped-query attention with biased projections, a rotation of neighbouring pairs on the first `rot_dims`
+    numbers of every head (frequencies base ** (-2 i / rot_dims), optionally stretched: `rot_scaling` =
+    (factor, low, high, original)), an RMS norm without weight on q and k after the rotation, and a learned softmax
+    sink per head."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot_dims: int
+    rot_base: float
+    rot_scaling: Optional[Tuple[float, float, float, float]] = None
+
+    @classmethod
+    def from_json(cls, m: dict) -> "RotaryAttentionConfig":
+        dim = int(m["dim"])
+        rot = m.get("rot") or {}
+        sc = rot.get("scaling")
+        c = cls(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=dim,
+                vdim=int(m.get("vdim", dim)), scale=float(m.get("scale", dim ** -0.5)),
+                rot_dims=int(rot.get("dims", 0) or 0), rot_base=float(rot.get("base", 10000.0)),
+                rot_scaling=None if not sc else (float(sc["factor"]), float(sc["low"]), float(sc["high"]),
+                                                 float(sc["original"])))
+        if c.heads % c.kv_heads or c.rot_dims % 2 or c.rot_dims > c.dim:
+            raise ValueError(f"attention: {c.heads} heads / {c.kv_heads} kv heads, rotation of {c.rot_dims} of {c.dim}")
+        return c
+
+
+@dataclass
+class DeltaRuleConfig:
+    """Gated delta rule (layers/recurrent.py): `heads` value heads of `vdim`, `kv_heads` query/key heads of `dim`,
+    a causal convolution of `conv` taps on q, k and v."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+
+    @classmethod
+    def from_json(cls, m: dict) -> "DeltaRuleConfig":
+        dim = int(m["dim"])
+        c = cls(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=dim,
+                vdim=int(m.get("vdim", dim)), conv=int(m.get("conv", 4)))
+        if c.heads % c.kv_heads or c.conv < 1:
+            raise ValueError(f"delta rule: {c.heads} heads / {c.kv_heads} kv heads, {c.conv} taps")
+        return c
+
+
+@dataclass
+class WkvConfig:
+    """Time mixing with a per-channel decay (layers/recurrent.py): `heads` heads of `dim` key and value channels.
+    `decay_rank` (the inner size of the decay's two-step projection) is not part of config.json: a checkpoint's
+    tensors give it; the default serves synthetic weights."""
+    heads: int
+    dim: int
+    decay_rank: int = 32
+
+    @classmethod
+    def from_json(cls, m: dict) -> "WkvConfig":
+        return cls(heads=int(m["heads"]), dim=int(m["dim"]), decay_rank=int(m.get("decay_rank", 32)))
+
+
+@dataclass
+class FafelixLayerConfig:
+    mixer_type: str                     # "attention" | "delta" | "wkv"
+    mixer: Any                          # RotaryAttentionConfig | DeltaRuleConfig | WkvConfig
+    mlp: Optional[FeedForwardConfig]    # dense, or None
+
+
+@dataclass
+class FafelixConfig:
+    """config.json of a Fafelix model: `vocab`, `width`, `norm.eps`, `embedding.bigram` (`buckets`, `mul_prev`,
+    `mul_cur`), `layers` (each with `type`, `mixer`, `mlp`), `loop` (`start`, `stop`, `times`).  Every layer is
+    x += mixer(h) + ff(h) with h = layer_norm(x); the looped span re-adds the embedding before each later pass."""
+    vocab_size: int
+    hidden_size: int
+    rms_norm_eps: float
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    layers: List[FafelixLayerConfig]
+    loop: Optional[Tuple[int, int, int]] = None
+    torch_dtype: Any = torch.bfloat16
+    max_position_embeddings: int = 1 << 30      # rotation angles are computed from the position: no table to outgrow
+    model_type: str = "fafelix"
+    tie_word_embeddings: bool = False
+    raw: dict = field(default_factory=dict, repr=False)
+
+    MIXERS = {"attention": RotaryAttentionConfig, "delta": DeltaRuleConfig, "wkv": WkvConfig}
+
+    @classmethod
+    def from_json(cls, c: dict) -> "FafelixConfig":
+        layers = []
+        for i, entry in enumerate(c["layers"]):
+            kind = entry["type"]
+            if kind not in cls.MIXERS:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            mlp = FeedForwardConfig.from_json(entry.get("mlp"))
+            if mlp is not None and mlp.kind != "dense":
+                raise ValueError(f"layer {i}: feed-forward kind {mlp.kind!r} is not part of this design")
+            layers.append(FafelixLayerConfig(kind, cls.MIXERS[kind].from_json(entry["mixer"]), mlp))
+        lp = c.get("loop")
+        loop = (int(lp["start"]), int(lp["stop"]), int(lp.get("times", 1))) if lp else None
+        if loop is not None and not (0 <= loop[0] <= loop[1] <= len(layers) and loop[2] >= 1):
+            raise ValueError(f"bad loop {loop} for {len(layers)} layers")
+        bg = (c.get("embedding") or {}).get("bigram")
+        if not bg:
+            raise ValueError("embedding.bigram is missing")
+        return cls(vocab_size=int(c["vocab"]), hidden_size=int(c["width"]),
+                   rms_norm_eps=float((c.get("norm") or {}).get("eps", 1e-6)), buckets=int(bg["buckets"]),
+                   mul_prev=int(bg["mul_prev"]), mul_cur=int(bg["mul_cur"]), layers=layers, loop=loop, raw=c)
+
+    @property
+    def layer_runs(self) -> List[Tuple[int, bool]]:
+        """(layer, re-add the embedding in front of it) in execution order; the flag marks the first layer of every
+        pass of the loop but the first."""
+        n = len(self.layers)
+        if self.loop is None:
+            return [(i, False) for i in range(n)]
+        start, stop, times = self.loop
+        runs = [(i, False) for i in range(start)]
+        for p in range(times):
+            runs += [(i, p > 0 and i == start) for i in range(start, stop)]
+        return runs + [(i, False) for i in range(stop, n)]
+
+    # ---- the names the cache manager and the runner read from an HF config --------------------------
+    def _attn(self):
+        return [l.mixer for l in self.layers if l.mixer_type == "attention"]
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.layer_runs)
+
+    @property
+    def num_key_value_heads(self) -> int:
+        return max([a.kv_heads for a in self._attn()] or [1])
+
+    @property
+    def num_attention_heads(self) -> int:
+        return max([a.heads for a in self._attn()] or [1])
+
+    @property
+    def head_dim(self) -> int:
+        return max([a.dim for a in self._attn()] or [1])
+
+
+ARCHITECTURES = {"Movolorn": MovolornConfig, "Batasun": BatasunConfig, "Fafelix": FafelixConfig}
 
 
 def load_model_config(path: str):

@@ -113,15 +113,41 @@ def linear_bias_slopes(num_heads: int, base_exponent: float = 8.0) -> torch.Tens
     return torch.pow(torch.tensor(2.0, dtype=torch.float64), -base_exponent * h / num_heads).float()
 
 
+def pair_rotation_frequencies(dims: int, base: float, scaling: Optional[tuple] = None) -> torch.Tensor:
+    """Rotation frequencies of dims / 2 pairs as 64-bit floats: f_i = base ** (-2 i / dims).  `scaling` =
+    (factor, low, high, original) stretches long wavelengths: with l = 2 pi / f, f stays where l < original / high,
+    becomes f / factor where l > original / low, and between the two is blended with
+    s = (original / l - low) / (high - low):  (1 - s) f / factor + s f."""
+    import math
+
+    out = []
+    for i in range(dims // 2):
+        f = float(base) ** (-2.0 * i / dims)
+        if scaling is not None:
+            factor, low, high, original = (float(v) for v in scaling)
+            wavelength = 2.0 * math.pi / f
+            if wavelength > original / low:
+                f = f / factor
+            elif wavelength >= original / high:
+                s = (original / wavelength - low) / (high - low)
+                f = (1.0 - s) * f / factor + s * f
+        out.append(f)
+    return torch.tensor(out, dtype=torch.float64)
+
+
 class BiasedChunkAttention(nn.Module):
     """Attention over the paged cache for models without rotation (csrc/bias_attn.cu):
 
         score(i, j) = scale * q_i . k_j - slopes[h] * (i - j),   j <= i and floor(i / chunk) == floor(j / chunk)
-        p_j = exp(score_j) / (sink + sum_j exp(score_j))
+        p_j = exp(score_j) / (sink * exp(sink_logits[h]) + sum_j exp(score_j))
 
-    with optional per-head RMS norm of q and k (weights shared by all heads), any head sizes (value size may differ
-    from the key size) and bfloat16 or float32 storage.  `slopes` None = no bias, `chunk` 0 = plain causal, `sink`
-    False = plain softmax.  forward() takes the packed projection rows [T, H*D + G*D + G*Dv]: one launch norms q / k
+    with optional per-head RMS norm of q and k (weights shared by all heads, or none), any head sizes (value size may
+    differ from the key size) and bfloat16 or float32 storage.  `slopes` None = no bias, `chunk` 0 = plain causal,
+    `sink` False = plain softmax; `learned_sink` gives every head its own sink score (a parameter, not scaled; without
+    it the score is 0).  `rotation` (inv_freq [rot_dims / 2] float64, see `pair_rotation_frequencies`) turns
+    neighbouring pairs (2 i, 2 i + 1) of the first rot_dims numbers of every q and k head by position * inv_freq[i]
+    BEFORE the norm; `norm` False leaves q and k unnormed.  forward() takes the packed projection rows
+    [T, H*D + G*D + G*Dv] (row stride free): one launch rotates / norms q / k
     and writes k / v to the cache at the tokens' positions, one launch attends — the portion kernel when any
     sequence of the step brings more than one token, the decode kernel otherwise.  The step's geometry comes from the
     global context: `positions_i32`, `token_slot`, `cu_seqlens_q`, `seq_start`, `batch_mapping`, `max_seqlen_q`.
@@ -129,8 +155,14 @@ class BiasedChunkAttention(nn.Module):
 
     def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float, *,
                  slopes: Optional[torch.Tensor] = None, chunk: int = 0, sink: bool = False, qk_norm: bool = False,
-                 eps: float = 1e-6, values_in_keys: bool = False):
+                 eps: float = 1e-6, values_in_keys: bool = False, learned_sink: bool = False,
+                 rotation: Optional[torch.Tensor] = None, norm: bool = True):
         super().__init__()
+        self.norm = bool(norm)
+        self.sink_logits = nn.Parameter(torch.zeros(num_heads, dtype=torch.float32)) if learned_sink else None
+        if rotation is not None:
+            assert rotation.dtype == torch.float64 and 2 * rotation.numel() <= head_dim
+        self.register_buffer("inv_freq", None if rotation is None else rotation.contiguous(), persistent=False)
         # values_in_keys: a value row is the first v_head_dim columns of its key row; there is no value cache
         self.values_in_keys = bool(values_in_keys)
         self.num_heads, self.num_kv_heads = int(num_heads), int(num_kv_heads)
@@ -174,10 +206,13 @@ class BiasedChunkAttention(nn.Module):
         q = torch.empty((T, H, D), dtype=qkv.dtype, device=dev)
         pt = self.page_table
         table = (N.ptr(pt), pt.stride(0), pt.stride(1), int(self.page_size))
-        N.check(lib.cvllm_qknorm_store(
-            N.ptr(qkv), qkv.stride(0), N.ptr(self.q_norm_weight), N.ptr(self.k_norm_weight), self.eps,
+        rot = self.inv_freq
+        N.check(lib.cvllm_rope_qknorm_store(
+            N.ptr(qkv), qkv.stride(0), N.ptr(rot), 0 if rot is None else 2 * rot.numel(), int(self.norm),
+            N.ptr(self.q_norm_weight), N.ptr(self.k_norm_weight), self.eps,
             N.ptr(ctx.positions_i32), N.ptr(ctx.token_slot), N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache),
-            *table, N.ptr(self.bh_seq_lens), T, H, G, D, Dv, RESERVED_BATCH, code, N.stream(dev)), "cvllm_qknorm_store")
+            *table, N.ptr(self.bh_seq_lens), T, H, G, D, Dv, RESERVED_BATCH, code, N.stream(dev)),
+            "cvllm_rope_qknorm_store")
         return self.attend(q)
 
     def attend(self, q: torch.Tensor, flat: bool = True) -> torch.Tensor:
@@ -206,7 +241,7 @@ class BiasedChunkAttention(nn.Module):
             N.check(lib.cvllm_bias_attn_varlen(
                 N.ptr(q), N.ptr(self.k_cache), N.ptr(v_cache), *table, N.ptr(ctx.cu_seqlens_q),
                 N.ptr(ctx.seq_start), N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink),
-                self.scale, N.ptr(out), B, int(ctx.max_seqlen_q), H, G, D, Dv, T, self.k_cache.shape[0], pt.shape[-1],
+                N.ptr(self.sink_logits), self.scale, N.ptr(out), B, int(ctx.max_seqlen_q), H, G, D, Dv, T, self.k_cache.shape[0], pt.shape[-1],
                 v_stride, code, N.stream(dev)), "cvllm_bias_attn_varlen")
         else:
             assert ctx.batch_mapping.numel() == T
@@ -214,8 +249,8 @@ class BiasedChunkAttention(nn.Module):
             ws = N.workspace(dev, 4 * T * H * splits * (2 + Dv), "bias_attn_decode") if splits > 1 else None
             N.check(lib.cvllm_bias_attn_decode(
                 N.ptr(q), N.ptr(self.k_cache), N.ptr(v_cache), *table, N.ptr(ctx.positions_i32),
-                N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink), self.scale, N.ptr(out),
-                T, H, G, D, Dv, RESERVED_BATCH, splits, N.ptr(ws), ws.numel() if ws is not None else 0, v_stride, code,
+                N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink), N.ptr(self.sink_logits),
+                self.scale, N.ptr(out), T, H, G, D, Dv, RESERVED_BATCH, splits, N.ptr(ws), ws.numel() if ws is not None else 0, v_stride, code,
                 N.stream(dev)), "cvllm_bias_attn_decode")
         if keep != Dv:
             out = out[:, :, :keep]

@@ -92,3 +92,51 @@ class NormWeight(nn.Module):
     def __init__(self, size: int) -> None:
         super().__init__()
         self.weight = nn.Parameter(torch.ones(size, dtype=torch.float32))
+
+
+NORM_RMS, NORM_LAYER = 0, 1
+
+
+def residual_norm(resid: torch.Tensor, *, add: tuple = (), add_f32: torch.Tensor | None = None,
+                  weight: torch.Tensor | None = None, bias: torch.Tensor | None = None, eps: float = 1e-6,
+                  kind: int = NORM_LAYER, out_dtype: torch.dtype | None = None):
+    """One launch of `cvllm_residual_norm` on a 32-bit residual stream `resid` [T, width], updated IN PLACE:
+
+        resid += add[0] + add[1] + add_f32      (up to two branch outputs in the activations' type, one fp32 tensor)
+        weight given:  returns norm(resid) in `out_dtype` - NORM_LAYER: (x - mean) / sqrt(var + eps) * weight + bias,
+                       NORM_RMS: x / sqrt(mean(x^2) + eps) * weight
+
+    i.e. the residual sum of a layer whose sublayers run side by side on one normed input, fused with the norm in
+    front of the next layer.  Sum and statistics are fp32; weight and bias are fp32 tensors."""
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.stride(1) == 1
+    rows, width = resid.shape
+    add = tuple(t for t in add if t is not None)
+    assert len(add) <= 2
+    a = add[0] if len(add) > 0 else None
+    b = add[1] if len(add) > 1 else None
+    ab_code = N.CVLLM_F32
+    for t in add:
+        assert t.shape == resid.shape and t.stride(1) == 1 and t.dtype == add[0].dtype
+        ab_code = N.block_dtype_code(t.dtype)
+    if add_f32 is not None:
+        assert add_f32.shape == resid.shape and add_f32.dtype == torch.float32 and add_f32.stride(1) == 1
+    out, o_code, o_stride = None, N.CVLLM_F32, 0
+    if weight is not None:
+        assert weight.dtype == torch.float32 and (bias is None or bias.dtype == torch.float32)
+        out = torch.empty((rows, width), dtype=out_dtype or torch.float32, device=resid.device)
+        o_code, o_stride = N.block_dtype_code(out.dtype), out.stride(0)
+    rc = N.lib().cvllm_residual_norm(
+        N.ptr(a), a.stride(0) if a is not None else 0, N.ptr(b), b.stride(0) if b is not None else 0, ab_code,
+        N.ptr(add_f32), add_f32.stride(0) if add_f32 is not None else 0, N.ptr(resid), resid.stride(0), N.ptr(weight),
+        N.ptr(bias), N.ptr(out), o_stride, o_code, rows, width, float(eps), int(kind), N.stream(resid.device))
+    N.check(rc, "cvllm_residual_norm")
+    return out
+
+
+class LayerNormWeight(nn.Module):
+    """Gain and bias of a layer norm kept in fp32 whatever the model dtype (the norm runs inside `residual_norm`)."""
+
+    def __init__(self, size: int) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(size, dtype=torch.float32))
+        self.bias = nn.Parameter(torch.zeros(size, dtype=torch.float32))

@@ -53,36 +53,78 @@ __device__ __forceinline__ int64_t cache_row(const PagedKV& c, int slot, int g, 
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// q / k norm + store.  One CTA per token; its warps take the token's H + 2G head rows in turn.
+// q / k rotation + norm + store.  One CTA per token; its warps take the token's H + 2G head rows in turn.
+// Rotation (inv_freq != NULL): neighbours (2i, 2i + 1) of the first rot_dims numbers of every q and k head turn by
+// pos * inv_freq[i] (64-bit angle, fp32 sine / cosine in shared memory, once per CTA) BEFORE the norm.
+// norm 0: no norm; 1: x / sqrt(mean(x^2) + eps), times the weight when one is given.
 // ---------------------------------------------------------------------------------------------------------
+struct Rotation {
+  const double* inv_freq;   // [dims / 2] or NULL (no rotation)
+  int dims;                 // even, <= D
+};
+
+// cos / sin of pos * inv_freq[i], i < dims / 2, into shared memory; the caller synchronises
+__device__ __forceinline__ void fill_rotation(float* cs, float* sn, const Rotation& rot, int pos) {
+  for (int i = threadIdx.x; i < rot.dims / 2; i += blockDim.x) {
+    double sv, cv;
+    sincos((double)pos * rot.inv_freq[i], &sv, &cv);
+    cs[i] = (float)cv;
+    sn[i] = (float)sv;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) qknorm_store_kernel(
     const T* __restrict__ qkv, int64_t qkv_stride, const float* __restrict__ q_w, const float* __restrict__ k_w,
     float eps, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_slot, T* __restrict__ q_out,
     T* __restrict__ k_cache, T* __restrict__ v_cache, PagedKV c, int32_t* __restrict__ bh_lens, int H, int G, int D,
-    int Dv, int reserved_slot) {
+    int Dv, int reserved_slot, Rotation rot, int norm) {
+  extern __shared__ float rot_cs[];   // cos [dims / 2], sin [dims / 2]
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = token_slot[t];
   const int pos = positions[t];
+  const int half = rot.inv_freq ? rot.dims / 2 : 0;
+  const float* cs = rot_cs;
+  const float* sn = rot_cs + half;
+  if (half > 0) {
+    fill_rotation(rot_cs, rot_cs + half, rot, pos);
+    __syncthreads();
+  }
   const T* row = qkv + (int64_t)t * qkv_stride;
+  const int pairs = (D + 1) / 2;
   for (int r = warp; r < H + 2 * G; r += 4) {
     if (r < H + G) {
       const bool is_q = r < H;
       const T* src = row + (int64_t)r * D;  // k heads follow the q heads with the same row size
       if (!is_q && slot == reserved_slot) continue;
+      // a lane takes pairs of neighbours, so that a rotated pair stays in one lane
+      auto pair_at = [&](int p, float& a, float& b) {
+        a = to_f<T>(src[2 * p]);
+        b = 2 * p + 1 < D ? to_f<T>(src[2 * p + 1]) : 0.f;
+        if (p < half) {
+          const float u = a, v = b;
+          a = u * cs[p] - v * sn[p];
+          b = v * cs[p] + u * sn[p];
+        }
+      };
       float ss = 0.f;
-      for (int d = lane; d < D; d += 32) {
-        const float x = to_f<T>(src[d]);
-        ss += x * x;
+      for (int p = lane; p < pairs; p += 32) {
+        float a, b;
+        pair_at(p, a, b);
+        ss += a * a + b * b;
       }
       ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-      const float* w = is_q ? q_w : k_w;
+      const float inv = norm ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
+      const float* w = norm ? (is_q ? q_w : k_w) : nullptr;
       T* dst = is_q ? q_out + ((int64_t)t * H + r) * D : k_cache + cache_row(c, slot, r - H, pos) * D;
-      for (int d = lane; d < D; d += 32) {
-        const float x = to_f<T>(src[d]) * inv;
-        dst[d] = from_f<T>(w ? x * w[d] : x);
+      for (int p = lane; p < pairs; p += 32) {
+        float a, b;
+        pair_at(p, a, b);
+        a *= inv;
+        b *= inv;
+        dst[2 * p] = from_f<T>(w ? a * w[2 * p] : a);
+        if (2 * p + 1 < D) dst[2 * p + 1] = from_f<T>(w ? b * w[2 * p + 1] : b);
       }
     } else {
       if (slot == reserved_slot) continue;
@@ -104,7 +146,7 @@ constexpr int BM = 64;
 template <typename T, int BN, int DVC>
 __global__ void __launch_bounds__(256) bias_attn_varlen_kernel(
     const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ seq_start,
-    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, float scale,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale,
     T* __restrict__ out, int H, int G, int D, int Dv) {
   constexpr int NJ = BN / 16;
   const int b = blockIdx.y, h = blockIdx.z;
@@ -136,7 +178,7 @@ __global__ void __launch_bounds__(256) bias_attn_varlen_kernel(
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     // with a sink the running maximum starts at the sink's score and the running sum with its term
-    m[i] = sink > 0.f ? 0.f : -INFINITY;
+    m[i] = sink > 0.f ? (sink_logits ? sink_logits[h] : 0.f) : -INFINITY;
     l[i] = sink;
 #pragma unroll
     for (int cc = 0; cc < DVC; ++cc) acc[i][cc] = 0.f;
@@ -270,7 +312,7 @@ template <int DMAX>
 __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
     const __nv_bfloat16* __restrict__ q, PagedKV c, const int32_t* __restrict__ cu_q,
     const int32_t* __restrict__ seq_start, const int32_t* __restrict__ batch_mapping,
-    const float* __restrict__ slopes, int chunk, float sink, float scale, __nv_bfloat16* __restrict__ out, int H, int G,
+    const float* __restrict__ slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, __nv_bfloat16* __restrict__ out, int H, int G,
     int D, int Dv) {
   constexpr int BN = 64, LD = DMAX + 8, KS = DMAX / 16, NV = DMAX / 8;
   constexpr float kL2e = 1.4426950408889634f;   // scores in log2 units: one ex2.approx per exponential
@@ -327,7 +369,7 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
   float m[2], l[2], o[NV][4];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    m[i] = sink > 0.f ? 0.f : -INFINITY;   // with a sink: its score and its term
+    m[i] = sink > 0.f ? (sink_logits ? sink_logits[h] * kL2e : 0.f) : -INFINITY;   // with a sink: its score and its term
     l[i] = sink;
   }
 #pragma unroll
@@ -462,14 +504,14 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
 
 template <int DMAX>
 int launch_varlen_mma(const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start, const int32_t* bm,
-                      const float* slopes, int chunk, float sink, float scale, void* out, int B, int max_new, int H,
+                      const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out, int B, int max_new, int H,
                       int G, int D, int Dv, cudaStream_t st) {
   static std::atomic<uint64_t> mask{0};
   const int smem = 4 * 64 * (DMAX + 8) * 2;
   auto kern = bias_attn_varlen_mma_kernel<DMAX>;
   CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), smem, mask));
   dim3 grid(cdiv(max_new, BM), B, H);
-  kern<<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), c, cu_q, seq_start, bm, slopes, chunk, sink,
+  kern<<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), c, cu_q, seq_start, bm, slopes, chunk, sink, sink_logits,
                                 scale, static_cast<__nv_bfloat16*>(out), H, G, D, Dv);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
@@ -486,7 +528,7 @@ constexpr int kDecCols = 16;  // output columns per lane: Dv <= 512
 template <typename T>
 __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
     const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ positions,
-    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, float scale,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale,
     T* __restrict__ out, int H, int G, int D, int Dv, int reserved_slot) {
   extern __shared__ float smem[];
   float* qs = smem;                         // [D]
@@ -548,9 +590,10 @@ __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
     if (col < Dv) mine[2 + col] = acc[cc];
   }
   __syncthreads();
-  float mm = sink > 0.f ? 0.f : -INFINITY;
+  const float sink_m = sink_logits ? sink_logits[h] : 0.f;   // the sink's score
+  float mm = sink > 0.f ? sink_m : -INFINITY;
   for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, part[w * (2 + Dv)]);
-  float ll = sink > 0.f ? sink * expf(0.f - mm) : 0.f;
+  float ll = sink > 0.f ? sink * expf(sink_m - mm) : 0.f;
   float f[kDecWarps];
   for (int w = 0; w < kDecWarps; ++w) {
     const float mw = part[w * (2 + Dv)];
@@ -624,11 +667,17 @@ __global__ void __launch_bounds__(128) qknorm_store_vec_kernel(
     const T* __restrict__ qkv, int64_t qkv_stride, const float* __restrict__ q_w, const float* __restrict__ k_w,
     float eps, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_slot, T* __restrict__ q_out,
     T* __restrict__ k_cache, T* __restrict__ v_cache, PagedKV c, int32_t* __restrict__ bh_lens, int H, int G, int D,
-    int Dv, int reserved_slot, int lpr) {
+    int Dv, int reserved_slot, int lpr, Rotation rot, int norm) {
+  extern __shared__ float rot_cs[];   // cos [dims / 2], sin [dims / 2]
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = token_slot[t];
   const int pos = positions[t];
+  const int half = rot.inv_freq ? rot.dims / 2 : 0;
+  if (half > 0) {
+    fill_rotation(rot_cs, rot_cs + half, rot, pos);
+    __syncthreads();
+  }
   const T* row = qkv + (int64_t)t * qkv_stride;
   const int rows_per_warp = 32 / lpr;
   const int r = (blockIdx.y * 4 + warp) * rows_per_warp + lane / lpr;
@@ -637,13 +686,24 @@ __global__ void __launch_bounds__(128) qknorm_store_vec_kernel(
   const bool stores = slot != reserved_slot;
   float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if ((is_q || (is_k && stores)) && cb < D) load8<T>(row + (int64_t)r * D + cb, x);
+  if (half > 0 && (is_q || is_k)) {   // the lane's four pairs of neighbours
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      const int p = (cb + e) >> 1;
+      if (p < half) {
+        const float u = x[e], v = x[e + 1];
+        x[e] = u * rot_cs[p] - v * rot_cs[half + p];
+        x[e + 1] = v * rot_cs[p] + u * rot_cs[half + p];
+      }
+    }
+  }
   float ss = 0.f;
 #pragma unroll
   for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
   for (int o = lpr >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // every lane takes part
   if ((is_q || (is_k && stores)) && cb < D) {
-    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-    const float* w = is_q ? q_w : k_w;
+    const float inv = norm ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
+    const float* w = norm ? (is_q ? q_w : k_w) : nullptr;
 #pragma unroll
     for (int e = 0; e < 8; ++e) x[e] = w ? x[e] * inv * w[cb + e] : x[e] * inv;
     T* dst = is_q ? q_out + ((int64_t)t * H + r) * D : k_cache + cache_row(c, slot, r - H, pos) * D;
@@ -663,7 +723,7 @@ __global__ void __launch_bounds__(128) qknorm_store_vec_kernel(
 template <typename T, int CH>
 __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
     const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ positions,
-    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, float scale,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale,
     T* __restrict__ out, float* __restrict__ part, int H, int G, int D, int Dv, int splits, int reserved_slot) {
   __shared__ float qs[kDecTile][64 * CH];
   __shared__ float st[4][kDecTile][2 + 64 * CH];
@@ -864,10 +924,11 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
   __syncthreads();
   for (int i = tid; i < nr * Dv; i += 128) {
     const int r = i / Dv, d = i - r * Dv;
-    float mm = (splits == 1 && sink > 0.f) ? 0.f : -INFINITY;
+    const float sink_m = sink_logits ? sink_logits[h0 + r] * 1.4426950408889634f : 0.f;   // the sink's score, log2 units
+    float mm = (splits == 1 && sink > 0.f) ? sink_m : -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) mm = fmaxf(mm, st[w][r][0]);
-    float ll = (splits == 1 && sink > 0.f) ? sink * ex2(0.f - mm) : 0.f, a = 0.f;
+    float ll = (splits == 1 && sink > 0.f) ? sink * ex2(sink_m - mm) : 0.f, a = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = st[w][r][0];
@@ -888,13 +949,15 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
 
 template <typename T>
 __global__ void __launch_bounds__(128) bias_attn_decode_merge_kernel(const float* __restrict__ part, float sink,
+                                                                     const float* __restrict__ sink_logits, int H,
                                                                      T* __restrict__ out, int Dv, int splits) {
   const int64_t bh = blockIdx.x;
   const int rec = 2 + Dv;
   const float* p = part + bh * splits * rec;
-  float mm = sink > 0.f ? 0.f : -INFINITY;
+  const float sink_m = sink_logits ? sink_logits[bh % H] * 1.4426950408889634f : 0.f;   // log2 units, as the parts
+  float mm = sink > 0.f ? sink_m : -INFINITY;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p[s * rec]);
-  float ll = sink > 0.f ? sink * ex2(0.f - mm) : 0.f;
+  float ll = sink > 0.f ? sink * ex2(sink_m - mm) : 0.f;
   for (int s = 0; s < splits; ++s)
     if (p[s * rec] != -INFINITY) ll += p[s * rec + 1] * ex2(p[s * rec] - mm);
   const float inv = ll > 0.f ? 1.0f / ll : 0.f;
@@ -908,14 +971,14 @@ __global__ void __launch_bounds__(128) bias_attn_decode_merge_kernel(const float
 
 template <typename T, int CH>
 int launch_decode_split_ch(const void* q, const PagedKV& c, const int32_t* positions, const int32_t* bm,
-                           const float* slopes, int chunk, float sink, float scale, void* out, float* part, dim3 grid,
+                           const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out, float* part, dim3 grid,
                            int H, int G, int D, int Dv, int splits, int reserved_slot, cudaStream_t st) {
   // the ring: stages x (K | V) x CH chunks x 16-byte pieces per chunk x 128 threads x 16 bytes
   const size_t ring = (size_t)(CH <= 2 ? 4 : 2) * 2 * CH * (8 / (16 / sizeof(T))) * 128 * 16;
   static std::atomic<uint64_t> mask{0};
   auto kern = bias_attn_decode_split_kernel<T, CH>;
   CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)ring, mask));
-  kern<<<grid, 128, ring, st>>>(static_cast<const T*>(q), c, positions, bm, slopes, chunk, sink, scale,
+  kern<<<grid, 128, ring, st>>>(static_cast<const T*>(q), c, positions, bm, slopes, chunk, sink, sink_logits, scale,
                                 static_cast<T*>(out), part, H, G, D, Dv, splits, reserved_slot);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
@@ -923,14 +986,14 @@ int launch_decode_split_ch(const void* q, const PagedKV& c, const int32_t* posit
 
 template <typename T>
 int launch_decode_split(const void* q, const PagedKV& c, const int32_t* positions, const int32_t* bm,
-                        const float* slopes, int chunk, float sink, float scale, void* out, float* part, int B, int H,
+                        const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out, float* part, int B, int H,
                         int G, int D, int Dv, int splits, int reserved_slot, cudaStream_t st) {
   const int R = H / G, tiles = cdiv(R, kDecTile);
   dim3 grid(splits, G * tiles, B);
   const int ch = cdiv(D > Dv ? D : Dv, 64);
   int rc;
 #define CVLLM_GO(CH) \
-  rc = launch_decode_split_ch<T, CH>(q, c, positions, bm, slopes, chunk, sink, scale, out, part, grid, H, G, D, Dv, \
+  rc = launch_decode_split_ch<T, CH>(q, c, positions, bm, slopes, chunk, sink, sink_logits, scale, out, part, grid, H, G, D, Dv, \
                                      splits, reserved_slot, st)
   if (ch == 1) CVLLM_GO(1);
   else if (ch == 2) CVLLM_GO(2);
@@ -939,7 +1002,7 @@ int launch_decode_split(const void* q, const PagedKV& c, const int32_t* position
 #undef CVLLM_GO
   if (rc != CVLLM_OK) return rc;
   if (splits > 1) {
-    bias_attn_decode_merge_kernel<T><<<B * H, 128, 0, st>>>(part, sink, static_cast<T*>(out), Dv, splits);
+    bias_attn_decode_merge_kernel<T><<<B * H, 128, 0, st>>>(part, sink, sink_logits, H, static_cast<T*>(out), Dv, splits);
     CVLLM_CHECK_LAUNCH();
   }
   return CVLLM_OK;
@@ -951,14 +1014,14 @@ size_t varlen_smem(int BN, int D, int Dv) {
 
 template <typename T, int BN, int DVC>
 int launch_varlen(const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start,
-                  const int32_t* batch_mapping, const float* slopes, int chunk, float sink, float scale, void* out,
+                  const int32_t* batch_mapping, const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out,
                   int B, int max_new, int H, int G, int D, int Dv, cudaStream_t st) {
   static std::atomic<uint64_t> mask{0};
   const size_t smem = varlen_smem(BN, D, Dv);
   auto kern = bias_attn_varlen_kernel<T, BN, DVC>;
   CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), 226 * 1024, mask));
   dim3 grid(cdiv(max_new, BM), B, H);
-  kern<<<grid, 256, smem, st>>>(static_cast<const T*>(q), c, cu_q, seq_start, batch_mapping, slopes, chunk, sink,
+  kern<<<grid, 256, smem, st>>>(static_cast<const T*>(q), c, cu_q, seq_start, batch_mapping, slopes, chunk, sink, sink_logits,
                                 scale, static_cast<T*>(out), H, G, D, Dv);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
@@ -966,10 +1029,10 @@ int launch_varlen(const void* q, const PagedKV& c, const int32_t* cu_q, const in
 
 template <typename T, int BN>
 int dispatch_dvc(int dvc, const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start,
-                 const int32_t* bm, const float* slopes, int chunk, float sink, float scale, void* out, int B,
+                 const int32_t* bm, const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out, int B,
                  int max_new, int H, int G, int D, int Dv, cudaStream_t st) {
 #define CVLLM_GO(N) \
-  return launch_varlen<T, BN, N>(q, c, cu_q, seq_start, bm, slopes, chunk, sink, scale, out, B, max_new, H, G, D, Dv, st)
+  return launch_varlen<T, BN, N>(q, c, cu_q, seq_start, bm, slopes, chunk, sink, sink_logits, scale, out, B, max_new, H, G, D, Dv, st)
   if (dvc <= 4) CVLLM_GO(4);
   if (dvc <= 6) CVLLM_GO(6);
   if (dvc <= 8) CVLLM_GO(8);
@@ -988,16 +1051,21 @@ using namespace cvllm;
 int cvllm_launch_prefill_bias(const void* q, const void* k_cache, const void* v_cache, int64_t cache_rows, void* out,
                               const int32_t* seq_start, const float* slopes, const int32_t* page_table,
                               const int32_t* batch_mapping, const int32_t* cu_seqlens_q, int B, int N, int HQ, int HKV,
-                              int PS, int NLP, int max_seqlen_q, float scale, int chunk, int sink, cudaStream_t st);
+                              int PS, int NLP, int max_seqlen_q, float scale, int chunk, int sink, const float* sink_logits,
+                              cudaStream_t st);
 
 static int check_dtype(int dtype) { return dtype == CVLLM_BF16 || dtype == CVLLM_F32; }
 
-extern "C" int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weight, const float* k_weight,
+static int rope_qknorm_store_impl(const double* inv_freq, int rot_dims, int norm, const void* qkv, int64_t qkv_stride, const float* q_weight, const float* k_weight,
                                   float eps, const int32_t* positions, const int32_t* token_slot, void* q_out,
                                   void* k_cache, void* v_cache, const int32_t* page_table, int64_t table_stride_slot,
                                   int64_t table_stride_head, int page_size, int32_t* bh_lens, int T, int H, int G,
                                   int D, int Dv, int reserved_slot, int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(T >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && page_size > 0);
+  CVLLM_CHECK_ARG(inv_freq == nullptr || (rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= D));
+  const Rotation rot{rot_dims > 0 ? inv_freq : nullptr, rot_dims};
+  const size_t rsmem = rot.inv_freq ? sizeof(float) * (size_t)rot_dims : 0;
+  CVLLM_CHECK_SUPPORTED(rsmem <= 32 * 1024);
   if (T == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(qkv && positions && token_slot && q_out && k_cache && v_cache && page_table && check_dtype(dtype));
   auto st = static_cast<cudaStream_t>(stream);
@@ -1011,38 +1079,60 @@ extern "C" int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const flo
     CVLLM_CHECK_SUPPORTED(T <= 2147483647 && cdiv(H + 2 * G, rows_per_cta) <= 65535);
     const dim3 grid(T, cdiv(H + 2 * G, rows_per_cta));
     if (dtype == CVLLM_BF16)
-      qknorm_store_vec_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
+      qknorm_store_vec_kernel<__nv_bfloat16><<<grid, 128, rsmem, st>>>(
           static_cast<const __nv_bfloat16*>(qkv), qkv_stride, q_weight, k_weight, eps, positions, token_slot,
           static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
-          static_cast<__nv_bfloat16*>(v_cache), c, bh_lens, H, G, D, Dv, reserved_slot, lpr);
+          static_cast<__nv_bfloat16*>(v_cache), c, bh_lens, H, G, D, Dv, reserved_slot, lpr, rot, norm);
     else
-      qknorm_store_vec_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(qkv), qkv_stride, q_weight,
+      qknorm_store_vec_kernel<float><<<grid, 128, rsmem, st>>>(static_cast<const float*>(qkv), qkv_stride, q_weight,
                                                            k_weight, eps, positions, token_slot,
                                                            static_cast<float*>(q_out), static_cast<float*>(k_cache),
                                                            static_cast<float*>(v_cache), c, bh_lens, H, G, D, Dv,
-                                                           reserved_slot, lpr);
+                                                           reserved_slot, lpr, rot, norm);
     CVLLM_CHECK_LAUNCH();
     return CVLLM_OK;
   }
   if (dtype == CVLLM_BF16)
-    qknorm_store_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(
+    qknorm_store_kernel<__nv_bfloat16><<<T, 128, rsmem, st>>>(
         static_cast<const __nv_bfloat16*>(qkv), qkv_stride, q_weight, k_weight, eps, positions, token_slot,
         static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
-        c, bh_lens, H, G, D, Dv, reserved_slot);
+        c, bh_lens, H, G, D, Dv, reserved_slot, rot, norm);
   else
-    qknorm_store_kernel<float><<<T, 128, 0, st>>>(static_cast<const float*>(qkv), qkv_stride, q_weight, k_weight, eps,
+    qknorm_store_kernel<float><<<T, 128, rsmem, st>>>(static_cast<const float*>(qkv), qkv_stride, q_weight, k_weight, eps,
                                                   positions, token_slot, static_cast<float*>(q_out),
                                                   static_cast<float*>(k_cache), static_cast<float*>(v_cache), c,
-                                                  bh_lens, H, G, D, Dv, reserved_slot);
+                                                  bh_lens, H, G, D, Dv, reserved_slot, rot, norm);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
+}
+
+
+extern "C" int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weight, const float* k_weight,
+                                  float eps, const int32_t* positions, const int32_t* token_slot, void* q_out,
+                                  void* k_cache, void* v_cache, const int32_t* page_table, int64_t table_stride_slot,
+                                  int64_t table_stride_head, int page_size, int32_t* bh_lens, int T, int H, int G,
+                                  int D, int Dv, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  return rope_qknorm_store_impl(nullptr, 0, 1, qkv, qkv_stride, q_weight, k_weight, eps, positions, token_slot, q_out,
+                                k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size, bh_lens,
+                                T, H, G, D, Dv, reserved_slot, dtype, stream);
+}
+
+extern "C" int cvllm_rope_qknorm_store(const void* qkv, int64_t qkv_stride, const double* inv_freq, int rot_dims,
+                                       int norm, const float* q_weight, const float* k_weight, float eps,
+                                       const int32_t* positions, const int32_t* token_slot, void* q_out, void* k_cache,
+                                       void* v_cache, const int32_t* page_table, int64_t table_stride_slot,
+                                       int64_t table_stride_head, int page_size, int32_t* bh_lens, int T, int H, int G,
+                                       int D, int Dv, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  return rope_qknorm_store_impl(inv_freq, rot_dims, norm, qkv, qkv_stride, q_weight, k_weight, eps, positions,
+                                token_slot, q_out, k_cache, v_cache, page_table, table_stride_slot, table_stride_head,
+                                page_size, bh_lens, T, H, G, D, Dv, reserved_slot, dtype, stream);
 }
 
 extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cache,
                                       const int32_t* page_table, int64_t table_stride_slot, int64_t table_stride_head,
                                       int page_size, const int32_t* cu_seqlens_q, const int32_t* seq_start,
                                       const int32_t* batch_mapping, const float* slopes, int chunk, int sink,
-                                      float scale, void* out, int B, int max_new, int H, int G, int D, int Dv,
+                                      const float* sink_logits, float scale, void* out, int B, int max_new, int H, int G, int D, int Dv,
                                       int total_tokens, int64_t cache_rows, int pages_per_head, int64_t v_stride,
                                       int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0);
@@ -1062,7 +1152,7 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
   while (bn > 32 && varlen_smem(bn, D, Dv) > cap) bn >>= 1;
   CVLLM_CHECK_SUPPORTED(varlen_smem(bn, D, Dv) <= cap);
 #define CVLLM_GO(T, BN) \
-  return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B, \
+  return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, sink_logits, scale, out, B, \
                              max_new, H, G, D, Dv, st)
   const int path = test_options().bias_attn_fma.load();   // 0 product, 1 fp32 FMA kernel, 2 no tcgen05 kernel
   if (dtype == CVLLM_BF16 && D == 128 && Dv == 128 && v_stride == Dv && page_size % 128 == 0 && (H / G) % 2 == 0 &&
@@ -1070,13 +1160,13 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
       table_stride_head == pages_per_head && table_stride_slot == (int64_t)G * pages_per_head && cache_rows > 0)
     return cvllm_launch_prefill_bias(q, k_cache, v_cache, cache_rows, out, seq_start, slopes, page_table,
                                      batch_mapping, cu_seqlens_q, B, total_tokens, H, G, page_size, pages_per_head,
-                                     max_new, scale, chunk, sink, st);
+                                     max_new, scale, chunk, sink, sink_logits, st);
   if (dtype == CVLLM_BF16 && D % 16 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && path != 1 &&
       v_stride % vec == 0 && aligned16(k_cache) && aligned16(v_cache)) {
     if (D <= 64 && Dv <= 64)
-      return launch_varlen_mma<64>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B,
+      return launch_varlen_mma<64>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, sink_logits, scale, out, B,
                                    max_new, H, G, D, Dv, st);
-    return launch_varlen_mma<128>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B,
+    return launch_varlen_mma<128>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, sink_logits, scale, out, B,
                                   max_new, H, G, D, Dv, st);
   }
   if (dtype == CVLLM_BF16) {
@@ -1091,8 +1181,8 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
 extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const void* v_cache,
                                       const int32_t* page_table, int64_t table_stride_slot, int64_t table_stride_head,
                                       int page_size, const int32_t* positions, const int32_t* batch_mapping,
-                                      const float* slopes, int chunk, int sink, float scale, void* out, int B, int H,
-                                      int G, int D, int Dv, int reserved_slot, int splits, float* workspace,
+                                      const float* slopes, int chunk, int sink, const float* sink_logits, float scale,
+                                      void* out, int B, int H, int G, int D, int Dv, int reserved_slot, int splits, float* workspace,
                                       size_t workspace_bytes, int64_t v_stride, int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(B >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0 && splits >= 1);
   if (B == 0) return CVLLM_OK;
@@ -1114,9 +1204,9 @@ extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const 
     }
     const float fs = sink ? 1.f : 0.f;
     if (dtype == CVLLM_BF16)
-      return launch_decode_split<__nv_bfloat16>(q, c, positions, batch_mapping, slopes, chunk, fs, scale, out,
+      return launch_decode_split<__nv_bfloat16>(q, c, positions, batch_mapping, slopes, chunk, fs, sink_logits, scale, out,
                                                 workspace, B, H, G, D, Dv, splits, reserved_slot, st);
-    return launch_decode_split<float>(q, c, positions, batch_mapping, slopes, chunk, fs, scale, out, workspace, B, H,
+    return launch_decode_split<float>(q, c, positions, batch_mapping, slopes, chunk, fs, sink_logits, scale, out, workspace, B, H,
                                       G, D, Dv, splits, reserved_slot, st);
   }
   const size_t smem = sizeof(float) * ((size_t)D + (size_t)kDecWarps * (2 + Dv));
@@ -1124,11 +1214,11 @@ extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const 
   dim3 grid(B, H);
   if (dtype == CVLLM_BF16)
     bias_attn_decode_kernel<__nv_bfloat16><<<grid, kDecWarps * 32, smem, st>>>(
-        static_cast<const __nv_bfloat16*>(q), c, positions, batch_mapping, slopes, chunk, sink ? 1.f : 0.f, scale,
+        static_cast<const __nv_bfloat16*>(q), c, positions, batch_mapping, slopes, chunk, sink ? 1.f : 0.f, sink_logits, scale,
         static_cast<__nv_bfloat16*>(out), H, G, D, Dv, reserved_slot);
   else
     bias_attn_decode_kernel<float><<<grid, kDecWarps * 32, smem, st>>>(
-        static_cast<const float*>(q), c, positions, batch_mapping, slopes, chunk, sink ? 1.f : 0.f, scale,
+        static_cast<const float*>(q), c, positions, batch_mapping, slopes, chunk, sink ? 1.f : 0.f, sink_logits, scale,
         static_cast<float*>(out), H, G, D, Dv, reserved_slot);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;

@@ -83,6 +83,88 @@ __global__ void __launch_bounds__(kThreads) sandwich_norm_kernel(
   for (int i = threadIdx.x; i < width; i += kThreads) o[i] = from_f<TO>(row[i] * inv * (w_pre[i] + gain_offset));
 }
 
+// One CTA per row of a 32-bit residual stream:
+//   resid += a + b + c     (a, b [rows, width] of type TY, c fp32; each may be NULL)
+//   out = norm(resid)      (out may be NULL: the sum alone)
+// KIND 0: resid / sqrt(mean(resid^2) + eps) * w;   KIND 1, layer norm: (resid - mean) / sqrt(var + eps) * w + bias with
+// var = the mean of the squared deviations (second pass over the row held in shared memory).  Sum, statistics and the
+// stream are fp32 whatever the activations' type.
+template <typename TY, typename TO, int KIND>
+__global__ void __launch_bounds__(kThreads) residual_norm_kernel(
+    const TY* __restrict__ a, int64_t a_stride, const TY* __restrict__ b, int64_t b_stride, const float* __restrict__ c,
+    int64_t c_stride, float* __restrict__ resid, int64_t r_stride, const float* __restrict__ w,
+    const float* __restrict__ bias, TO* __restrict__ out, int64_t o_stride, int width, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[kThreads / 32];
+  const int64_t r = blockIdx.x;
+  float* res = resid + r * r_stride;
+  const bool sums = a != nullptr || b != nullptr || c != nullptr;
+  float s1 = 0.f;
+  for (int i = threadIdx.x; i < width; i += kThreads) {
+    float v = res[i];
+    if (a != nullptr) v += to_f<TY>(a[r * a_stride + i]);
+    if (b != nullptr) v += to_f<TY>(b[r * b_stride + i]);
+    if (c != nullptr) v += c[r * c_stride + i];
+    if (sums) res[i] = v;
+    row[i] = v;
+    s1 += KIND == 1 ? v : v * v;
+  }
+  if (out == nullptr) return;
+  TO* o = out + r * o_stride;
+  s1 = block_sum(s1, red);
+  if constexpr (KIND == 0) {
+    const float inv = 1.0f / sqrtf(s1 / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += kThreads) o[i] = from_f<TO>(row[i] * inv * w[i]);
+  } else {
+    const float mean = s1 / (float)width;
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < width; i += kThreads) {   // every thread reads back what it wrote itself
+      const float d = row[i] - mean;
+      s2 += d * d;
+    }
+    s2 = block_sum(s2, red);
+    const float inv = 1.0f / sqrtf(s2 / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += kThreads)
+      o[i] = from_f<TO>((row[i] - mean) * inv * w[i] + (bias ? bias[i] : 0.f));
+  }
+}
+
+// Token embedding plus a hashed embedding of the (previous token, token) pair, one CTA per token:
+//   out[t, :] = embed[id_t, :] + pair[row_t, :],   row_t = (prev_t * mul_prev + id_t * mul_cur) mod buckets,
+// and row_t = buckets (the table's extra last row) for a sequence's first token (position 0).  prev_t is the token
+// before t in the step when that one belongs to the same sequence (same slot, position one less), else the slot's
+// entry of prev_state (the last token of the sequence's previous step).  fp32 sum of the two rows.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) pair_embed_kernel(
+    const int64_t* __restrict__ ids, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_slot,
+    const T* __restrict__ embed, const T* __restrict__ pair, int64_t buckets, int64_t mul_prev, int64_t mul_cur,
+    const int32_t* __restrict__ prev_state, float* __restrict__ out, int64_t o_stride, int width) {
+  const int t = blockIdx.x;
+  const int64_t id = ids[t];
+  const int pos = positions[t], slot = token_slot[t];
+  int64_t prow = buckets;
+  if (pos > 0) {
+    int64_t prev;
+    if (t > 0 && token_slot[t - 1] == slot && positions[t - 1] == pos - 1) prev = ids[t - 1];
+    else prev = prev_state[slot];
+    prow = (prev * mul_prev + id * mul_cur) % buckets;
+  }
+  const T* e = embed + id * width;
+  const T* pr = pair + prow * width;
+  float* o = out + (int64_t)t * o_stride;
+  for (int i = threadIdx.x; i < width; i += kThreads) o[i] = to_f<T>(e[i]) + to_f<T>(pr[i]);
+}
+
+// prev_state[slot] = the last token each sequence brings in this step (runs after pair_embed_kernel has read the old one)
+__global__ void pair_state_update_kernel(const int64_t* __restrict__ ids, const int32_t* __restrict__ token_slot,
+                                         int32_t* __restrict__ prev_state, int T, int reserved_slot) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const int slot = token_slot[t];
+  if (slot == reserved_slot) return;
+  if (t == T - 1 || token_slot[t + 1] != slot) prev_state[slot] = (int32_t)ids[t];
+}
+
 __device__ __forceinline__ float act_silu(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float act_gelu_tanh(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -359,6 +441,57 @@ extern "C" int cvllm_sandwich_norm(const void* y, int64_t y_stride, int y_dtype,
   else CVLLM_SANDWICH(float, float);
 #undef CVLLM_SANDWICH
   CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_residual_norm(const void* a, int64_t a_stride, const void* b, int64_t b_stride, int ab_dtype,
+                                   const float* c, int64_t c_stride, float* resid, int64_t r_stride, const float* w,
+                                   const float* bias, void* out, int64_t o_stride, int out_dtype, int rows, int width,
+                                   float eps, int kind, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(rows >= 0 && width > 0 && resid && (kind == 0 || kind == 1));
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG((a == nullptr && b == nullptr) || ab_dtype == CVLLM_BF16 || ab_dtype == CVLLM_F32);
+  CVLLM_CHECK_ARG(out == nullptr || (w != nullptr && (out_dtype == CVLLM_BF16 || out_dtype == CVLLM_F32)));
+  CVLLM_CHECK_SUPPORTED(width <= 12288);
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)width * sizeof(float);
+  const bool yb = ab_dtype == CVLLM_BF16 && (a || b), ob = out_dtype == CVLLM_BF16;
+#define CVLLM_RESNORM(TY, TO, KIND)                                                                                \
+  residual_norm_kernel<TY, TO, KIND><<<rows, kThreads, smem, st>>>(                                                \
+      static_cast<const TY*>(a), a_stride, static_cast<const TY*>(b), b_stride, c, c_stride, resid, r_stride, w,    \
+      bias, static_cast<TO*>(out), o_stride, width, eps)
+#define CVLLM_RESNORM_K(TY, TO) \
+  do { if (kind == 0) CVLLM_RESNORM(TY, TO, 0); else CVLLM_RESNORM(TY, TO, 1); } while (0)
+  if (yb && ob) CVLLM_RESNORM_K(__nv_bfloat16, __nv_bfloat16);
+  else if (yb) CVLLM_RESNORM_K(__nv_bfloat16, float);
+  else if (ob) CVLLM_RESNORM_K(float, __nv_bfloat16);
+  else CVLLM_RESNORM_K(float, float);
+#undef CVLLM_RESNORM_K
+#undef CVLLM_RESNORM
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_pair_hash_embed(const int64_t* ids, const int32_t* positions, const int32_t* token_slot,
+                                     const void* embed, const void* pair, int64_t buckets, int64_t mul_prev,
+                                     int64_t mul_cur, int32_t* prev_state, float* out, int64_t out_stride, int T,
+                                     int width, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(T >= 0 && width > 0 && buckets > 0);
+  if (T == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(ids && positions && token_slot && embed && pair && prev_state && out);
+  CVLLM_CHECK_ARG(dtype == CVLLM_BF16 || dtype == CVLLM_F32);
+  auto st = static_cast<cudaStream_t>(stream);
+  if (dtype == CVLLM_BF16)
+    pair_embed_kernel<__nv_bfloat16><<<T, kThreads, 0, st>>>(ids, positions, token_slot,
+                                                             static_cast<const __nv_bfloat16*>(embed),
+                                                             static_cast<const __nv_bfloat16*>(pair), buckets, mul_prev,
+                                                             mul_cur, prev_state, out, out_stride, width);
+  else
+    pair_embed_kernel<float><<<T, kThreads, 0, st>>>(ids, positions, token_slot, static_cast<const float*>(embed),
+                                                     static_cast<const float*>(pair), buckets, mul_prev, mul_cur,
+                                                     prev_state, out, out_stride, width);
+  pair_state_update_kernel<<<cdiv(T, 256), 256, 0, st>>>(ids, token_slot, prev_state, T, reserved_slot);
+  CVLLM_CHECK_LAUNCHES(2);
   return CVLLM_OK;
 }
 

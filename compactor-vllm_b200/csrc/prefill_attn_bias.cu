@@ -35,7 +35,8 @@ struct PrefillBiasParams {
   float scale_log2;
   float rescale_threshold;
   int chunk;                  // 0 = no chunking
-  float sink;                 // 1 = a sink of score 0 in the denominator, 0 = none
+  float sink;                 // 1 = a sink in the denominator, 0 = none
+  const float* sink_logits;   // [HQ] the sink's score per head, or NULL (score 0)
 };
 
 struct PrefillBiasSmem {
@@ -291,7 +292,9 @@ prefill_attn_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     const bool row_valid = (q0 + row) < La;
     const uint32_t s_tmem = tmem + t * kBN + lane_base;
     const uint32_t o_tmem = tmem + 256 + t * kHD + lane_base;
-    float m_ref = p.sink > 0.f ? 0.f : -INFINITY, l = p.sink;   // a sink: its score and its term
+    // a sink: its score (log2 units, like every score here) and its term
+    float m_ref = p.sink > 0.f ? (p.sink_logits ? p.sink_logits[hq0 + t] * 1.4426950408889634f : 0.f) : -INFINITY;
+    float l = p.sink;
     const int pi = p0 + row;                                   // this thread's query position
     const int lo_i = p.chunk > 0 ? (pi / p.chunk) * p.chunk : 0;
     const int lo_max = p.chunk > 0 ? (p_last / p.chunk) * p.chunk : 0;
@@ -473,7 +476,8 @@ using namespace cvllm;
 int cvllm_launch_prefill_bias(const void* q, const void* k_cache, const void* v_cache, int64_t cache_rows, void* out,
                               const int32_t* seq_start, const float* slopes, const int32_t* page_table,
                               const int32_t* batch_mapping, const int32_t* cu_seqlens_q, int B, int N, int HQ, int HKV,
-                              int PS, int NLP, int max_seqlen_q, float scale, int chunk, int sink, cudaStream_t st) {
+                              int PS, int NLP, int max_seqlen_q, float scale, int chunk, int sink, const float* sink_logits,
+                              cudaStream_t st) {
   using namespace pb;
   CVLLM_CHECK_ALIGN(aligned16(q) && aligned16(out) && aligned16(k_cache) && aligned16(v_cache));
   CUtensorMap tm_q, tm_kc, tm_vc;
@@ -504,6 +508,7 @@ int cvllm_launch_prefill_bias(const void* q, const void* k_cache, const void* v_
   }
   p.chunk = chunk;
   p.sink = sink ? 1.f : 0.f;
+  p.sink_logits = sink ? sink_logits : nullptr;
   const size_t smem = sizeof(PrefillBiasSmem) + 1024;
   const dim3 grid((max_seqlen_q + kBM - 1) / kBM, HQ / 2, B);
   static std::atomic<uint64_t> attr_bf{0};

@@ -414,6 +414,25 @@ int cvllm_sandwich_norm(const void* y, int64_t y_stride, int y_dtype, const floa
                         int64_t r_stride, const float* w_pre, void* out, int64_t o_stride, int out_dtype,
                         int rows, int width, float eps, float gain_offset, int assign, cvllm_stream_t stream);
 
+/* One launch per residual update of a 32-bit stream, rows independent:
+ *   resid += a + b + c   (a, b [rows, width] of ab_dtype, c fp32 [rows, width]; each may be NULL)
+ *   out = norm(resid)    (out may be NULL: the sum alone); kind 0: resid / sqrt(mean(resid^2) + eps) * w;
+ *   kind 1, layer norm: (resid - mean) / sqrt(var + eps) * w + bias, var = the mean of the squared deviations
+ *   (bias may be NULL).  w, bias fp32.  width <= 12288.  Strides in elements. */
+int cvllm_residual_norm(const void* a, int64_t a_stride, const void* b, int64_t b_stride, int ab_dtype,
+                        const float* c, int64_t c_stride, float* resid, int64_t r_stride, const float* w,
+                        const float* bias, void* out, int64_t o_stride, int out_dtype, int rows, int width, float eps,
+                        int kind, cvllm_stream_t stream);
+
+/* out[t, :] (fp32) = embed[ids[t], :] + pair[row_t, :] with row_t = (prev_t * mul_prev + ids[t] * mul_cur) mod buckets,
+ * and row_t = buckets (the table's extra last row) where positions[t] == 0.  prev_t = ids[t - 1] when token t - 1 of
+ * the step has the same slot and the position before, else prev_state[token_slot[t]]; afterwards prev_state[slot] =
+ * the last token the slot brought in this step (reserved_slot excepted).  embed [V, width], pair [buckets + 1, width]. */
+int cvllm_pair_hash_embed(const int64_t* ids, const int32_t* positions, const int32_t* token_slot, const void* embed,
+                          const void* pair, int64_t buckets, int64_t mul_prev, int64_t mul_cur, int32_t* prev_state,
+                          float* out, int64_t out_stride, int T, int width, int reserved_slot, int dtype,
+                          cvllm_stream_t stream);
+
 /* Packed [gate | up] rows -> out[t, f]; kind 0: silu(gate) * up, 1: gelu_tanh(gate) * up, 2: the clamped gated unit
  * g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1).  limit is read by kind 2 only. */
 int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64_t o_stride, int64_t rows, int F, int kind,
@@ -449,7 +468,8 @@ int cvllm_expert_gemv(const void* xs, int x_div, const void* w, const int32_t* i
  * Biased attention over the paged cache (csrc/bias_attn.cu): any head size, CVLLM_BF16 or CVLLM_F32 storage,
  * fp32 arithmetic.  score(i, j) = scale * q_i . k_j - slopes[h] * (i - j) for j <= i with
  * floor(i / chunk) == floor(j / chunk) (chunk 0: no chunking; slopes NULL: no bias);
- * p_j = exp(s_j) / (sink + sum exp(s_j)), sink 0 or 1.  Positions count from the start of each sequence.
+ * p_j = exp(s_j) / (sink * exp(sink_logits[h]) + sum exp(s_j)), sink 0 or 1; sink_logits [H] fp32 is the sink's score
+ * per head (not scaled; NULL = 0).  Positions count from the start of each sequence.
  * The cache is the one of the store path: k_cache [rows, D], v_cache [rows, Dv], page_table[slot, head, page]
  * with the two strides given, page_size rows per page.  v_stride (elements between value rows; 0 = Dv) lets the
  * values be a column range of wider rows, e.g. v_cache = k_cache with v_stride = D: the first Dv columns of the keys.
@@ -464,6 +484,16 @@ int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weigh
                        int64_t table_stride_head, int page_size, int32_t* bh_lens, int T, int H, int G, int D,
                        int Dv, int reserved_slot, int dtype, cvllm_stream_t stream);
 
+/* The same with a rotation in front of the norm: inv_freq [rot_dims / 2] doubles (NULL = none); neighbours
+ * (2 i, 2 i + 1) of the first rot_dims numbers of every q and k head turn by positions[t] * inv_freq[i].
+ * norm 0: no norm at all; 1: the RMS norm above (weights may be NULL). */
+int cvllm_rope_qknorm_store(const void* qkv, int64_t qkv_stride, const double* inv_freq, int rot_dims, int norm,
+                            const float* q_weight, const float* k_weight, float eps, const int32_t* positions,
+                            const int32_t* token_slot, void* q_out, void* k_cache, void* v_cache,
+                            const int32_t* page_table, int64_t table_stride_slot, int64_t table_stride_head,
+                            int page_size, int32_t* bh_lens, int T, int H, int G, int D, int Dv, int reserved_slot,
+                            int dtype, cvllm_stream_t stream);
+
 /* Portions: sequence b brings tokens cu_seqlens_q[b] .. cu_seqlens_q[b+1]-1 at positions seq_start[b] + 0, 1, ...;
  * all their keys (and every earlier one) are in the cache of slot batch_mapping[b].  out [T, H, Dv].
  * max_new = the largest number of new tokens of one sequence, total_tokens = T, cache_rows = rows of k_cache,
@@ -473,8 +503,9 @@ int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weigh
 int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
                            int64_t table_stride_slot, int64_t table_stride_head, int page_size,
                            const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* batch_mapping,
-                           const float* slopes, int chunk, int sink, float scale, void* out, int B, int max_new,
-                           int H, int G, int D, int Dv, int total_tokens, int64_t cache_rows, int pages_per_head,
+                           const float* slopes, int chunk, int sink, const float* sink_logits, float scale, void* out,
+                           int B, int max_new, int H, int G, int D, int Dv, int total_tokens, int64_t cache_rows,
+                           int pages_per_head,
                            int64_t v_stride, int dtype, cvllm_stream_t stream);
 
 /* Decode: one query per sequence at position positions[b] (its key is in the cache already).  q [B, H, D],
@@ -484,7 +515,8 @@ int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cac
 int cvllm_bias_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
                            int64_t table_stride_slot, int64_t table_stride_head, int page_size,
                            const int32_t* positions, const int32_t* batch_mapping, const float* slopes, int chunk,
-                           int sink, float scale, void* out, int B, int H, int G, int D, int Dv, int reserved_slot,
+                           int sink, const float* sink_logits, float scale, void* out, int B, int H, int G, int D, int Dv,
+                           int reserved_slot,
                            int splits, float* workspace, size_t workspace_bytes, int64_t v_stride, int dtype,
                            cvllm_stream_t stream);
 
@@ -550,6 +582,41 @@ int cvllm_ssm_scan(const float* xbc, int64_t xbc_stride, const void* proj, int64
 int cvllm_gated_group_norm(const float* y, int64_t y_stride, const void* z, int64_t z_stride, const float* weight,
                            float eps, void* out, int64_t out_stride, int64_t rows, int width, int parts, int dtype,
                            cvllm_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Mixers with a [key, value] matrix state per head (csrc/recurrent.cu).  Step geometry as for the state-space mixer.
+ * Both recurrences end, inside the kernel, with each head's unit norm, a weight and a gate:
+ *   out[t, h * Dv + j] = o / sqrt(mean_j(o^2) + eps) * norm_w[h * norm_head_stride + j] * silu(gate[t, gate_off + h * Dv + j])
+ * (norm_head_stride 0: one weight vector shared by the heads).  state [slots, H, D, Dv] fp32.  D, Dv <= 256.
+ * --------------------------------------------------------------------- */
+
+/* out[s, t, :] = h[t] + (h[t - 1] - h[t]) * mu[s, :] for s < S (out [S, total_tokens, W], model type, mu fp32 [S, W]);
+ * the row before a portion's first comes from shift_state [slots, W] (zeros at position 0), which then takes the
+ * portion's last row. */
+int cvllm_token_shift_mix(const void* h, int64_t h_stride, const float* mu, int S, int W, void* shift_state,
+                          const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                          const int32_t* batch_mapping, int B, int max_new, void* out, int64_t total_tokens,
+                          int reserved_slot, int dtype, cvllm_stream_t stream);
+
+/* Gated delta rule.  qkv [T, 2 G D + H Dv] fp32 = (q | k | v) after the short convolution; q and k are made unit
+ * vectors per head (x / sqrt(sum x^2 + 1e-6)), q times D^-1/2; beta = sigmoid(proj[t, b_off + h]);
+ * g = exp(-exp(A_log[h]) * softplus(proj[t, a_off + h] + dt_bias[h])); per head
+ *   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.   Head h reads q / k head h / (H / G). */
+int cvllm_delta_rule(const float* qkv, int64_t qkv_stride, const void* proj, int64_t proj_stride, int b_off, int a_off,
+                     const float* A_log, const float* dt_bias, float* state, const void* gate, int64_t gate_stride,
+                     int gate_off, const float* norm_w, int norm_head_stride, float eps, const int32_t* cu_seqlens_q,
+                     const int32_t* seq_start, const int32_t* positions, const int32_t* batch_mapping, int B,
+                     int max_new, void* out, int64_t out_stride, int H, int G, int D, int Dv, int reserved_slot,
+                     int dtype, cvllm_stream_t stream);
+
+/* wkv: r, k, v, w_raw rows of H * D numbers (model type); w = exp(-exp(w_raw + w0)) per head and key channel;
+ *   o = (S + diag(bonus_h) k v^T)^T r;  S <- diag(w) S + k v^T.   Dv = D. */
+int cvllm_wkv_scan(const void* r, int64_t r_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
+                   const void* w_raw, int64_t w_stride, const float* w0, const float* bonus, float* state,
+                   const void* gate, int64_t gate_stride, int gate_off, const float* norm_w, int norm_head_stride,
+                   float eps, const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                   const int32_t* batch_mapping, int B, int max_new, void* out, int64_t out_stride, int H, int D,
+                   int reserved_slot, int dtype, cvllm_stream_t stream);
 
 #ifdef __cplusplus
 }
