@@ -381,9 +381,10 @@ class FafelixConfig:
             kind = entry["type"]
             if kind not in cls.MIXERS:
                 raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
-            mlp = FeedForwardConfig.from_json(entry.get("mlp"))
-            if mlp is not None and mlp.kind != "dense":
-                raise ValueError(f"layer {i}: feed-forward kind {mlp.kind!r} is not part of this design")
+            ff = entry.get("mlp")
+            if ff is not None and ff.get("kind", "dense") != "dense":
+                raise ValueError(f"layer {i}: feed-forward kind {ff.get('kind')!r} is not part of this design")
+            mlp = FeedForwardConfig.from_json(ff)
             layers.append(FafelixLayerConfig(kind, cls.MIXERS[kind].from_json(entry["mixer"]), mlp))
         lp = c.get("loop")
         loop = (int(lp["start"]), int(lp["stop"]), int(lp.get("times", 1))) if lp else None

@@ -251,3 +251,6 @@ class FafelixForCausalLM(nn.Module):
             else:
                 val = val * (p.shape[-1] ** -0.5)
             p.copy_(val.to(p.dtype))
+        for layer in self.layers:      # the feed-forward's columns of the shared input projection have no bias
+            if layer.in_proj is not None and layer.in_proj.bias is not None:
+                layer.in_proj.bias[layer.mixer.in_cols:].zero_()

@@ -448,6 +448,7 @@ extern "C" int cvllm_residual_norm(const void* a, int64_t a_stride, const void* 
                                    const float* c, int64_t c_stride, float* resid, int64_t r_stride, const float* w,
                                    const float* bias, void* out, int64_t o_stride, int out_dtype, int rows, int width,
                                    float eps, int kind, cvllm_stream_t stream) {
+  drop_stale_error();
   CVLLM_CHECK_ARG(rows >= 0 && width > 0 && resid && (kind == 0 || kind == 1));
   if (rows == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG((a == nullptr && b == nullptr) || ab_dtype == CVLLM_BF16 || ab_dtype == CVLLM_F32);
@@ -476,6 +477,7 @@ extern "C" int cvllm_pair_hash_embed(const int64_t* ids, const int32_t* position
                                      const void* embed, const void* pair, int64_t buckets, int64_t mul_prev,
                                      int64_t mul_cur, int32_t* prev_state, float* out, int64_t out_stride, int T,
                                      int width, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
   CVLLM_CHECK_ARG(T >= 0 && width > 0 && buckets > 0);
   if (T == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(ids && positions && token_slot && embed && pair && prev_state && out);

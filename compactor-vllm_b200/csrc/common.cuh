@@ -62,6 +62,11 @@ void note_launches(int n);
   } while (0)
 #define CVLLM_CHECK_LAUNCH() CVLLM_CHECK_LAUNCHES(1)
 
+// A library call in front of an entry (a vendor GEMM that tried and dropped a kernel variant, say) can leave a
+// non-sticky error behind that nobody read; the launch check above would then blame the next launch for it.  Entries
+// that run right behind library calls start by reading it away.  Sticky errors (faults) stay and are still reported.
+inline void drop_stale_error() { (void)cudaGetLastError(); }
+
 // cudaFuncAttributeMaxDynamicSharedMemorySize is a per-DEVICE property of a kernel: raise it once per
 // (kernel, device), so one process can drive several GPUs.  `mask` (one static per call site) has a
 // bit per device ordinal.  Not a stream operation: safe under CUDA-graph capture.

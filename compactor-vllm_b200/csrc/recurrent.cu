@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(256) token_shift_update_kernel(const T* __rest
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kTok = 16;   // tokens staged at a time
 constexpr int KS = 4;      // slices of the key dimension
+constexpr int kMaxValueDim = 256;
 
 template <int R>
 struct Lay {
@@ -365,8 +366,10 @@ template <typename T, int R, int MAXT>
 int launch_delta(dim3 grid, int threads, size_t smem, cudaStream_t st, const float* qkv, int64_t qkv_stride,
                  const void* proj, int64_t proj_stride, int b_off, int a_off, const float* A_log, const float* dt_bias,
                  int G, const RecurArgs& a) {
+  // the attribute is set once per kernel: to what the largest value row needs, not to this launch's size
   static std::atomic<uint64_t> attr{0};
-  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)delta_rule_kernel<T, R, MAXT>, (int)smem, attr));
+  constexpr int kMaxSmem = (int)sizeof(float) * (2 * kTok * KS * (R + 4) + 2 * kTok * kMaxValueDim + kTok * 4);
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)delta_rule_kernel<T, R, MAXT>, kMaxSmem, attr));
   delta_rule_kernel<T, R, MAXT><<<grid, threads, smem, st>>>(qkv, qkv_stride, static_cast<const T*>(proj), proj_stride,
                                                              b_off, a_off, A_log, dt_bias, G, a);
   CVLLM_CHECK_LAUNCH();
@@ -378,7 +381,8 @@ int launch_wkv(dim3 grid, int threads, size_t smem, cudaStream_t st, const void*
                int64_t k_stride, const void* v, int64_t v_stride, const void* w_raw, int64_t w_stride, const float* w0,
                const float* bonus, const RecurArgs& a) {
   static std::atomic<uint64_t> attr{0};
-  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)wkv_scan_kernel<T, R, MAXT>, (int)smem, attr));
+  constexpr int kMaxSmem = (int)sizeof(float) * (3 * kTok * KS * (R + 4) + 2 * kTok * kMaxValueDim);
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)wkv_scan_kernel<T, R, MAXT>, kMaxSmem, attr));
   wkv_scan_kernel<T, R, MAXT><<<grid, threads, smem, st>>>(static_cast<const T*>(r), r_stride, static_cast<const T*>(k),
                                                            k_stride, static_cast<const T*>(v), v_stride,
                                                            static_cast<const T*>(w_raw), w_stride, w0, bonus, a);
@@ -399,6 +403,7 @@ extern "C" int cvllm_token_shift_mix(const void* h, int64_t h_stride, const floa
                                      const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
                                      const int32_t* batch_mapping, int B, int max_new, void* out, int64_t total_tokens,
                                      int reserved_slot, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
   CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && S > 0 && W > 0);
   if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(h && mu && shift_state && batch_mapping && out && recur_dtype_ok(dtype));
@@ -440,12 +445,13 @@ extern "C" int cvllm_delta_rule(const float* qkv, int64_t qkv_stride, const void
                                 const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
                                 const int32_t* batch_mapping, int B, int max_new, void* out, int64_t out_stride, int H,
                                 int G, int D, int Dv, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
   CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0);
   if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(qkv && proj && A_log && dt_bias && state && gate && norm_w && batch_mapping && out &&
                   recur_dtype_ok(dtype));
   CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
-  CVLLM_CHECK_SUPPORTED(D <= 256 && Dv <= 256 && H <= 65535 && B <= 65535);
+  CVLLM_CHECK_SUPPORTED(D <= 256 && Dv <= kMaxValueDim && H <= 65535 && B <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
   const int R = slice_rows(D), threads = recur_threads(Dv);
   const size_t smem = sizeof(float) * ((size_t)2 * kTok * KS * (R + 4) + (size_t)2 * kTok * Dv + kTok * 4);
@@ -466,12 +472,13 @@ extern "C" int cvllm_wkv_scan(const void* r, int64_t r_stride, const void* k, in
                               const int32_t* seq_start, const int32_t* positions, const int32_t* batch_mapping, int B,
                               int max_new, void* out, int64_t out_stride, int H, int D, int reserved_slot, int dtype,
                               cvllm_stream_t stream) {
+  drop_stale_error();
   CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && D > 0);
   if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(r && k && v && w_raw && w0 && bonus && state && gate && norm_w && batch_mapping && out &&
                   recur_dtype_ok(dtype));
   CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
-  CVLLM_CHECK_SUPPORTED(D <= 256 && H <= 65535 && B <= 65535);
+  CVLLM_CHECK_SUPPORTED(D <= kMaxValueDim && H <= 65535 && B <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
   const int R = slice_rows(D), threads = recur_threads(D);
   const size_t smem = sizeof(float) * ((size_t)3 * kTok * KS * (R + 4) + (size_t)2 * kTok * D);

@@ -223,3 +223,45 @@ def forward(model, tokens, collect=None):
         if collect is not None:
             collect.append(x.clone())
     return layer_norm(x, model["final_norm"], model["final_norm_b"], eps) @ _d(model["head"]).T
+
+
+def from_checkpoint(cfg: dict, tensors: dict) -> dict:
+    """The oracle's model dict from a config.json dict and the checkpoint's tensors by name."""
+    f = lambda name: tensors[name].float()
+    bg = cfg["embedding"]["bigram"]
+    lp = cfg.get("loop")
+    model = {"embed": f("embed"), "bigram": f("bigram"), "buckets": bg["buckets"], "mul_prev": bg["mul_prev"],
+             "mul_cur": bg["mul_cur"], "eps": cfg["norm"]["eps"], "final_norm": f("final.norm"),
+             "final_norm_b": f("final.norm.b"), "head": f("head"), "layers": [],
+             "loop": (lp["start"], lp["stop"], lp["times"]) if lp else None}
+    for i, entry in enumerate(cfg["layers"]):
+        p = f"l{i}."
+        m = dict(entry["mixer"])
+        m["type"] = entry["type"]
+        g = lambda name: f(p + "mix." + name)
+        if entry["type"] == "attention":
+            rot = m.pop("rot", None) or {}
+            sc = rot.get("scaling")
+            m.update(rot_dims=rot.get("dims", 0), rot_base=rot.get("base", 10000.0),
+                     rot_scaling=(sc["factor"], sc["low"], sc["high"], sc["original"]) if sc else None)
+            m.setdefault("kv_heads", m["heads"])
+            m.setdefault("vdim", m["dim"])
+            for n in "qkv":
+                m[n], m[n + "_b"] = g(n), g(n + ".b")
+            m["sink"], m["o"] = g("sink"), g("o")
+        elif entry["type"] == "delta":
+            m.setdefault("kv_heads", m["heads"])
+            m.setdefault("vdim", m["dim"])
+            for n in "qkv":
+                m[n], m[n + "_conv"] = g(n), g(n + ".conv")
+            for n in ("b", "a", "A_log", "dt_bias", "g", "norm", "o"):
+                m[n] = g(n)
+        else:
+            m["mu"] = {n: g("mu." + n) for n in "rkvgw"}
+            for n in ("r", "k", "v", "g", "w1", "w2", "w0", "u", "norm", "o"):
+                m[n] = g(n)
+        mlp = None
+        if entry.get("mlp") is not None:
+            mlp = {n: f(p + "mlp." + n) for n in ("gate", "up", "down")}
+        model["layers"].append({"norm1": f(p + "norm1"), "norm1_b": f(p + "norm1.b"), "mixer": m, "mlp": mlp})
+    return model
