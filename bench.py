@@ -743,7 +743,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="only the headline step (for ncu runs)")
     ap.add_argument("--only-cfg5", action="store_true", help=argparse.SUPPRESS)
-    ap.add_argument("--arch", default=None, choices=["movolorn", "batasun"],
+    ap.add_argument("--arch", default=None, choices=["movolorn", "batasun", "fafelix"],
                     help="instead of the headline workload: prefill / decode throughput of this model design beside "
                          "the closest existing model at equal size, and its kernels against the measured peaks")
     ap.add_argument("--arch-sizes", default="1b-like,8b-like", help="with --arch: comma-separated size names")
@@ -753,6 +753,8 @@ def main():
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
         if args.arch == "batasun":
             from compactor_vllm.benchmarks import batasun_compare as arch_compare
+        elif args.arch == "fafelix":
+            from compactor_vllm.benchmarks import fafelix_compare as arch_compare
         else:
             from compactor_vllm.benchmarks import arch_compare
 
