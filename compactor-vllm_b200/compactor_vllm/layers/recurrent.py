@@ -74,7 +74,7 @@ class DeltaRuleMixer(nn.Module):
 
     def make_state(self) -> MixerState:
         return MixerState({"conv_state": ((max(self.taps - 1, 1), self.conv_channels), None),
-                           "matrix_state": ((self.heads, self.dim, self.vdim), torch.float32)})
+                           "matrix_state": ((self.heads, self.vdim, self.dim), torch.float32)})   # [value, key]
 
     def forward(self, h: torch.Tensor, cols: torch.Tensor, state: MixerState) -> torch.Tensor:
         """cols [T, in_cols] (row stride free): this mixer's columns of the projection of h."""
@@ -127,7 +127,7 @@ class WkvMixer(nn.Module):
 
     def make_state(self) -> MixerState:
         return MixerState({"shift_state": ((self.width,), None),
-                           "matrix_state": ((self.heads, self.dim, self.dim), torch.float32)})
+                           "matrix_state": ((self.heads, self.dim, self.dim), torch.float32)})    # [value, key]
 
     def forward(self, h: torch.Tensor, cols: Optional[torch.Tensor], state: MixerState) -> torch.Tensor:
         ctx = get_context()

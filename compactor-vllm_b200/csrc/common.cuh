@@ -98,6 +98,7 @@ struct TestOptions {
   std::atomic<int> grs_rows_per_round{0};     // > 0: rows per reduce round of gemm_reduce (multiple of 256)
   std::atomic<int> bias_attn_fma{0};          // 1: 16-bit portions of the biased attention on the fp32 FMA kernel
   std::atomic<int> ssm_segment{0};            // > 0: tokens per segment of the state-space scan (0: chosen per step)
+  std::atomic<int> recur_layout{0};           // > 0: 100 * CTAs per (head, sequence) + register slice of the matrix-state mixers (0: chosen per step)
 };
 TestOptions& test_options();
 

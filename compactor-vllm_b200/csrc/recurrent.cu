@@ -15,11 +15,9 @@
 // replays).  A portion that starts at position 0 starts from a zero state whatever the slot holds.  States, decays,
 // gates of the recurrence, norms and the outputs before the final rounding are fp32.
 //
-// Recurrence kernels: CTA = (head, sequence); thread (j, s) keeps rows s * R .. s * R + R - 1 of column j of the state in
-// registers (KS = 4 slices of the key dimension, padded to DK = 4 R rows; padded rows stay zero), so a token costs R
-// multiply-adds per dot product and two shuffles to sum the slices.  Tokens are staged kTok at a time in shared
-// memory (keys in the padded slice layout, read as 16-byte broadcasts); the outputs of those tokens wait there for
-// the norm, which runs once per stage with a warp per token.
+// Recurrence kernels: a cluster of up to four CTAs per (head, sequence), the state in registers; see below.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace cvllm {
@@ -108,27 +106,45 @@ __global__ void __launch_bounds__(256) token_shift_update_kernel(const T* __rest
 
 // ---------------------------------------------------------------------------------------------------------
 // Recurrences.
+// A cluster of VT CTAs serves one (head, sequence): CTA v keeps value columns v * CW .. v * CW + CW - 1 of the state.
+// Thread (j, s) keeps rows s * R .. s * R + R - 1 of column j in registers (KS slices of the key dimension, a power of
+// two with KS * R >= D; rows beyond D stay zero), so a token costs R multiply-adds per dot product and log2(KS)
+// shuffles to sum the slices.  Tokens are staged `tok` at a time in shared memory (key-sized rows in a padded slice
+// layout, read as 16-byte broadcasts); the outputs of those tokens wait there for the unit norm, which runs once per
+// stage with a warp per token: every CTA sums the squares of its own columns, the cluster exchanges the partial sums
+// through distributed shared memory (one cluster barrier per stage, two buffers), and every CTA writes its columns.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kTok = 16;   // tokens staged at a time
-constexpr int KS = 4;      // slices of the key dimension
+constexpr int kTokMax = 64;   // most tokens staged at a time (a step's count: RecurArgs::tok)
+
 constexpr int kMaxValueDim = 256;
+constexpr int kMaxKeyDim = 256;
+constexpr int kMaxSlices = 32;
 
 template <int R>
 struct Lay {
   static constexpr int SL = R + 4;        // floats per slice in shared memory (the pad keeps 16-byte loads conflict-free)
-  static constexpr int ROW = KS * SL;     // floats per staged key-sized row
   __device__ static __forceinline__ int at(int i) { return (i / R) * SL + (i % R); }
 };
 
-__device__ __forceinline__ float slice_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
+__device__ __forceinline__ float slice_sum(float v, int KS) {
+  for (int o = KS >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// a thread's slice (R numbers) of a staged key-sized row, as 16-byte loads
+template <int R>
+__device__ __forceinline__ void load_slice(float (&dst)[R], const float* row_slice) {
+  const float4* p = reinterpret_cast<const float4*>(row_slice);
+#pragma unroll
+  for (int r = 0; r < R; r += 4) {
+    const float4 t = p[r / 4];
+    dst[r] = t.x; dst[r + 1] = t.y; dst[r + 2] = t.z; dst[r + 3] = t.w;
+  }
 }
 
 struct RecurArgs {
   StepGeom g;
-  float* state;            // [slots, H, D, Dv]
+  float* state;            // [slots, H, Dv, D]: a value column's key rows are contiguous, as a thread's slice is
   const void* gate;        // [T, ..] model type: gate logits of (token, head, value channel) at gate_off + h * Dv + j
   int64_t gate_stride;
   int gate_off;
@@ -138,45 +154,106 @@ struct RecurArgs {
   void* out;               // [T, ..] model type, head h at columns h * Dv
   int64_t out_stride;
   int H, D, Dv, reserved_slot;
+  int KS, VT, CW;          // slices of the key dimension; CTAs per (head, sequence); value columns per CTA
+  int tok;                 // tokens staged at a time
 };
 
-// the outputs of `n` staged tokens (so [kTok][Dv] fp32) -> unit norm per token, weight, gate, rounded to the model type
+// (row, col) of the elements e = threadIdx.x + u * blockDim.x, u = 0, 1, .., of a tile [rows, width]: one division at
+// the start, additions afterwards
+struct TileWalk {
+  int c, d, step_c, step_d, width;
+  __device__ __forceinline__ TileWalk(int width_) : width(width_) {
+    c = threadIdx.x / width_;
+    d = threadIdx.x - c * width_;
+    step_c = blockDim.x / width_;
+    step_d = blockDim.x - step_c * width_;
+  }
+  __device__ __forceinline__ void next() {
+    c += step_c;
+    d += step_d;
+    if (d >= width) { d -= width; ++c; }
+  }
+};
+
+constexpr int kPF = 8;    // key-sized elements a thread prefetches per staged array (the rest is loaded at commit time)
+constexpr int kPFG = 4;   // gate logits a thread prefetches per stage
+
+// gate logits of the stage's (token, column) elements e = tid + u * blockDim.x, e = c * ncol + j, loaded ahead of use
 template <typename T>
-__device__ __forceinline__ void gated_unit_norm_rows(const RecurArgs& a, const float* so, int h, int tok0, int n) {
+__device__ __forceinline__ void prefetch_gates(const RecurArgs& a, T (&pg)[kPFG], int h, int c0, int ncol, int tok0,
+                                               int n) {
+  const T* gate = static_cast<const T*>(a.gate);
+  TileWalk w(ncol);
+#pragma unroll
+  for (int u = 0; u < kPFG; ++u, w.next())
+    if (w.c < n) pg[u] = gate[(int64_t)(tok0 + w.c) * a.gate_stride + a.gate_off + h * a.Dv + c0 + w.d];
+}
+
+// The outputs of `n` staged tokens (so [tok][CW] fp32, this CTA's columns c0 .. c0 + ncol - 1) -> unit norm per token
+// over ALL Dv columns of the head, weight, gate, rounded to the model type.  part [2][kTokMax]: this CTA's sums of squares,
+// read by the other CTAs of the cluster (`stage` picks the buffer); sinv [kTokMax]: the tokens' 1 / rms.  Every CTA of the
+// cluster calls this the same number of times (they share the sequence), so the cluster barrier inside is matched.
+template <typename T>
+__device__ __forceinline__ void gated_unit_norm_rows(const RecurArgs& a, const float* so, float* part, float* sinv,
+                                                     int stage, const T (&pg)[kPFG], int h, int c0, int ncol, int tok0,
+                                                     int n) {
+  namespace cg = cooperative_groups;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const T* gate = static_cast<const T*>(a.gate);
   T* out = static_cast<T*>(a.out);
+  float* mine = part + (stage & 1) * kTokMax;
   for (int c = warp; c < n; c += warps) {
-    const float* o = so + c * a.Dv;
+    const float* o = so + c * a.CW;
     float ss = 0.f;
-    for (int j = lane; j < a.Dv; j += 32) ss += o[j] * o[j];
+    for (int j = lane; j < ncol; j += 32) ss += o[j] * o[j];
     ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)a.Dv + a.eps);
-    const int64_t t = tok0 + c;
-    for (int j = lane; j < a.Dv; j += 32) {
-      const float gz = to_f<T>(gate[t * a.gate_stride + a.gate_off + h * a.Dv + j]);
-      out[t * a.out_stride + h * a.Dv + j] = from_f<T>(o[j] * inv * a.norm_w[h * a.norm_head_stride + j] * silu_f(gz));
-    }
+    if (lane == 0) mine[c] = ss;
   }
+  if (a.VT > 1) cg::this_cluster().sync();
+  else __syncthreads();
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float ss = 0.f;
+    if (a.VT > 1) {
+      cg::cluster_group cl = cg::this_cluster();
+      for (int v = 0; v < a.VT; ++v) ss += cl.map_shared_rank(mine, v)[c];
+    } else {
+      ss = mine[c];
+    }
+    sinv[c] = 1.0f / sqrtf(ss / (float)a.Dv + a.eps);
+  }
+  __syncthreads();
+  auto emit = [&](int c, int j, float gz) {
+    const int col = h * a.Dv + c0 + j;
+    out[(int64_t)(tok0 + c) * a.out_stride + col] =
+        from_f<T>(so[c * a.CW + j] * sinv[c] * a.norm_w[h * a.norm_head_stride + c0 + j] * silu_f(gz));
+  };
+  TileWalk w(ncol);
+#pragma unroll
+  for (int u = 0; u < kPFG; ++u, w.next())
+    if (w.c < n) emit(w.c, w.d, to_f<T>(pg[u]));
+  for (; w.c < n; w.next())
+    emit(w.c, w.d, to_f<T>(gate[(int64_t)(tok0 + w.c) * a.gate_stride + a.gate_off + h * a.Dv + c0 + w.d]));
 }
 
 template <int R>
-__device__ __forceinline__ void load_state(float (&S)[R], const RecurArgs& a, int slot, int h, int j, int ks, bool from_pool) {
+__device__ __forceinline__ void load_state(float (&S)[R], const RecurArgs& a, int slot, int h, int col, bool valid,
+                                           int ks, bool from_pool) {
   const float* src = a.state + ((int64_t)slot * a.H + h) * a.D * a.Dv;
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int i = ks * R + r;
-    S[r] = (from_pool && j < a.Dv && i < a.D) ? src[(int64_t)i * a.Dv + j] : 0.f;
+    S[r] = (from_pool && valid && i < a.D) ? src[(int64_t)col * a.D + i] : 0.f;
   }
 }
 
 template <int R>
-__device__ __forceinline__ void store_state(const float (&S)[R], const RecurArgs& a, int slot, int h, int j, int ks) {
+__device__ __forceinline__ void store_state(const float (&S)[R], const RecurArgs& a, int slot, int h, int col,
+                                            bool valid, int ks) {
   float* dst = a.state + ((int64_t)slot * a.H + h) * a.D * a.Dv;
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int i = ks * R + r;
-    if (j < a.Dv && i < a.D) dst[(int64_t)i * a.Dv + j] = S[r];
+    if (valid && i < a.D) dst[(int64_t)col * a.D + i] = S[r];
   }
 }
 
@@ -192,44 +269,85 @@ __global__ void __launch_bounds__(MAXT) delta_rule_kernel(const float* __restric
                                                           const float* __restrict__ dt_bias, int G, RecurArgs a) {
   using L = Lay<R>;
   extern __shared__ __align__(16) float sm[];
-  const int D = a.D, Dv = a.Dv, H = a.H;
+  const int D = a.D, Dv = a.Dv, H = a.H, KS = a.KS, CW = a.CW, kTok = a.tok;
+  const int ROW = KS * L::SL;
   float* sq = sm;                       // [kTok][ROW]
-  float* sk = sq + kTok * L::ROW;       // [kTok][ROW]
-  float* sv = sk + kTok * L::ROW;       // [kTok][Dv]
-  float* so = sv + kTok * Dv;           // [kTok][Dv]
-  float* sc = so + kTok * Dv;           // [kTok][4]: decay, beta, k . q
-  const int h = blockIdx.x, b = blockIdx.y;
+  float* sk = sq + kTok * ROW;          // [kTok][ROW]
+  float* sv = sk + kTok * ROW;          // [kTok][CW]
+  float* so = sv + kTok * CW;           // [kTok][CW]
+  float* sc = so + kTok * CW;           // [kTok][4]: decay, beta, k . q
+  float* part = sc + kTok * 4;          // [2][kTokMax]
+  float* sinv = part + 2 * kTokMax;     // [kTokMax]
+  const int h = blockIdx.x / a.VT, vt = blockIdx.x % a.VT, b = blockIdx.y;
   int t0, n_new, start;
   portion(a.g, b, t0, n_new, start);
-  if (n_new <= 0) return;
+  if (n_new <= 0) return;               // the same for every CTA of the cluster
   const int slot = a.g.slots[b];
   const int kvh = h / (H / G);
+  const int c0 = vt * CW, ncol = min(CW, Dv - c0);
   const int tid = threadIdx.x, j = tid / KS, ks = tid % KS;
+  const bool valid = j < ncol;
   const int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
-  for (int i = tid; i < 2 * kTok * L::ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
+  for (int i = tid; i < 2 * kTok * ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
   float S[R];
-  load_state<R>(S, a, slot, h, j, ks, start > 0);
+  load_state<R>(S, a, slot, h, c0 + j, valid, ks, start > 0);
   const float neg_a = -expf(A_log[h]), dtb = dt_bias[h];
   const float q_scale = rsqrtf((float)D);
-  const int q_col = kvh * D, k_col = G * D + kvh * D, v_col = 2 * G * D + h * Dv;
+  const int q_col = kvh * D, k_col = G * D + kvh * D, v_col = 2 * G * D + h * Dv + c0;
   __syncthreads();
-  for (int j0 = 0; j0 < n_new; j0 += kTok) {
+  // a stage's inputs are loaded into registers one stage ahead, so that their latency hides behind the tokens before
+  float pq[kPF], pk[kPF], pv[kPFG];
+  T pg[kPFG];
+  auto prefetch = [&](int j0n) {
+    const int nn = min(kTok, n_new - j0n);
+    TileWalk w(D);
+#pragma unroll
+    for (int u = 0; u < kPF; ++u, w.next())
+      if (w.c < nn) {
+        const float* row = qkv + (int64_t)(t0 + j0n + w.c) * qkv_stride;
+        pq[u] = row[q_col + w.d];
+        pk[u] = row[k_col + w.d];
+      }
+    TileWalk wv(ncol);
+#pragma unroll
+    for (int u = 0; u < kPFG; ++u, wv.next())
+      if (wv.c < nn) pv[u] = qkv[(int64_t)(t0 + j0n + wv.c) * qkv_stride + v_col + wv.d];
+  };
+  prefetch(0);
+  int stage = 0;
+  for (int j0 = 0; j0 < n_new; j0 += kTok, ++stage) {
     const int n = min(kTok, n_new - j0);
-    for (int i = tid; i < n * D; i += blockDim.x) {
-      const int c = i / D, d = i - c * D;
-      const float* row = qkv + (int64_t)(t0 + j0 + c) * qkv_stride;
-      sq[c * L::ROW + L::at(d)] = row[q_col + d];
-      sk[c * L::ROW + L::at(d)] = row[k_col + d];
+    {
+      TileWalk w(D);
+#pragma unroll
+      for (int u = 0; u < kPF; ++u, w.next())
+        if (w.c < n) {
+          sq[w.c * ROW + L::at(w.d)] = pq[u];
+          sk[w.c * ROW + L::at(w.d)] = pk[u];
+        }
+      for (; w.c < n; w.next()) {
+        const float* row = qkv + (int64_t)(t0 + j0 + w.c) * qkv_stride;
+        sq[w.c * ROW + L::at(w.d)] = row[q_col + w.d];
+        sk[w.c * ROW + L::at(w.d)] = row[k_col + w.d];
+      }
+      TileWalk wv(ncol);
+#pragma unroll
+      for (int u = 0; u < kPFG; ++u, wv.next())
+        if (wv.c < n) sv[wv.c * CW + wv.d] = pv[u];
+      for (; wv.c < n; wv.next()) sv[wv.c * CW + wv.d] = qkv[(int64_t)(t0 + j0 + wv.c) * qkv_stride + v_col + wv.d];
     }
-    for (int i = tid; i < n * Dv; i += blockDim.x) {
-      const int c = i / Dv, d = i - c * Dv;
-      sv[c * Dv + d] = qkv[(int64_t)(t0 + j0 + c) * qkv_stride + v_col + d];
+    for (int c = tid; c < n; c += blockDim.x) {   // the tokens' decays and betas
+      const T* pr = proj + (int64_t)(t0 + j0 + c) * proj_stride;
+      sc[c * 4 + 0] = expf(neg_a * softplus_f(to_f<T>(pr[a_off + h]) + dtb));
+      sc[c * 4 + 1] = sigmoid_f(to_f<T>(pr[b_off + h]));
     }
     __syncthreads();
+    if (j0 + kTok < n_new) prefetch(j0 + kTok);
+    prefetch_gates<T>(a, pg, h, c0, ncol, t0 + j0, n);
     for (int c = warp; c < n; c += warps) {   // unit q and k, the token's scalars
       float qq = 0.f, kk = 0.f, qk = 0.f;
       for (int d = lane; d < D; d += 32) {
-        const float qv = sq[c * L::ROW + L::at(d)], kv = sk[c * L::ROW + L::at(d)];
+        const float qv = sq[c * ROW + L::at(d)], kv = sk[c * ROW + L::at(d)];
         qq += qv * qv;
         kk += kv * kv;
         qk += qv * kv;
@@ -239,49 +357,56 @@ __global__ void __launch_bounds__(MAXT) delta_rule_kernel(const float* __restric
       qk = warp_sum(qk);
       const float qi = q_scale / sqrtf(qq + 1e-6f), ki = 1.0f / sqrtf(kk + 1e-6f);
       for (int d = lane; d < D; d += 32) {
-        sq[c * L::ROW + L::at(d)] *= qi;
-        sk[c * L::ROW + L::at(d)] *= ki;
+        sq[c * ROW + L::at(d)] *= qi;
+        sk[c * ROW + L::at(d)] *= ki;
       }
-      if (lane == 0) {
-        const T* pr = proj + (int64_t)(t0 + j0 + c) * proj_stride;
-        sc[c * 4 + 0] = expf(neg_a * softplus_f(to_f<T>(pr[a_off + h]) + dtb));
-        sc[c * 4 + 1] = sigmoid_f(to_f<T>(pr[b_off + h]));
-        sc[c * 4 + 2] = qk * qi * ki;
-      }
+      if (lane == 0) sc[c * 4 + 2] = qk * qi * ki;
     }
     __syncthreads();
-    for (int c = 0; c < n; ++c) {
-      const float4* q4 = reinterpret_cast<const float4*>(sq + c * L::ROW + ks * L::SL);
-      const float4* k4 = reinterpret_cast<const float4*>(sk + c * L::ROW + ks * L::SL);
-      float dk = 0.f, dq = 0.f;
-#pragma unroll
-      for (int r = 0; r < R; r += 4) {
-        const float4 kq = k4[r / 4], qq = q4[r / 4];
-        dk = fmaf(S[r], kq.x, dk); dq = fmaf(S[r], qq.x, dq);
-        dk = fmaf(S[r + 1], kq.y, dk); dq = fmaf(S[r + 1], qq.y, dq);
-        dk = fmaf(S[r + 2], kq.z, dk); dq = fmaf(S[r + 2], qq.z, dq);
-        dk = fmaf(S[r + 3], kq.w, dk); dq = fmaf(S[r + 3], qq.w, dq);
+    // One token: its key / query slices are in registers already (loaded while the token before ran); the next token's
+    // are requested first.  Four partial sums per dot product keep the multiply-add chains short.
+    auto step = [&](const float (&kc)[R], const float (&qc)[R], float (&kn)[R], float (&qn)[R], int c, bool ahead) {
+      if (ahead && c + 1 < n) {
+        load_slice<R>(kn, sk + (c + 1) * ROW + ks * L::SL);
+        load_slice<R>(qn, sq + (c + 1) * ROW + ks * L::SL);
       }
-      dk = slice_sum(dk);
-      dq = slice_sum(dq);
       const float gd = sc[c * 4 + 0], beta = sc[c * 4 + 1], kq_dot = sc[c * 4 + 2];
-      const float vj = j < Dv ? sv[c * Dv + j] : 0.f;
-      const float u = beta * (vj - gd * dk);
-      if (ks == 0 && j < Dv) so[c * Dv + j] = fmaf(kq_dot, u, gd * dq);
+      const float vj = valid ? sv[c * CW + j] : 0.f;
+      float dk[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < R; r += 4) {
-        const float4 kq = k4[r / 4];
-        S[r] = fmaf(kq.x, u, gd * S[r]);
-        S[r + 1] = fmaf(kq.y, u, gd * S[r + 1]);
-        S[r + 2] = fmaf(kq.z, u, gd * S[r + 2]);
-        S[r + 3] = fmaf(kq.w, u, gd * S[r + 3]);
+      for (int r = 0; r < R; ++r) {
+        dk[r & 3] = fmaf(S[r], kc[r], dk[r & 3]);
+        dq[r & 3] = fmaf(S[r], qc[r], dq[r & 3]);
+      }
+      const float dks = slice_sum((dk[0] + dk[1]) + (dk[2] + dk[3]), KS);
+      const float dqs = slice_sum((dq[0] + dq[1]) + (dq[2] + dq[3]), KS);
+      const float u = beta * (vj - gd * dks);
+      if (ks == 0 && valid) so[c * CW + j] = fmaf(kq_dot, u, gd * dqs);
+#pragma unroll
+      for (int r = 0; r < R; ++r) S[r] = fmaf(kc[r], u, gd * S[r]);
+    };
+    if constexpr (R <= 16) {
+      float ka[R], qa[R], kb[R], qb[R];
+      load_slice<R>(ka, sk + ks * L::SL);
+      load_slice<R>(qa, sq + ks * L::SL);
+      for (int c = 0; c < n; c += 2) {
+        step(ka, qa, kb, qb, c, true);
+        if (c + 1 < n) step(kb, qb, ka, qa, c + 1, true);
+      }
+    } else {   // long slices: no registers to spare for the token ahead
+      float ka[R], qa[R];
+      for (int c = 0; c < n; ++c) {
+        load_slice<R>(ka, sk + c * ROW + ks * L::SL);
+        load_slice<R>(qa, sq + c * ROW + ks * L::SL);
+        step(ka, qa, ka, qa, c, false);
       }
     }
     __syncthreads();
-    gated_unit_norm_rows<T>(a, so, h, t0 + j0, n);
+    gated_unit_norm_rows<T>(a, so, part, sinv, stage, pg, h, c0, ncol, t0 + j0, n);
     __syncthreads();
   }
-  if (slot != a.reserved_slot) store_state<R>(S, a, slot, h, j, ks);
+  if (slot != a.reserved_slot) store_state<R>(S, a, slot, h, c0 + j, valid, ks);
+  if (a.VT > 1) cooperative_groups::this_cluster().sync();   // nobody leaves while its sums may still be read
 }
 
 // wkv.  r, k, v: [T, H * D] rows of the model type (row strides given); w_raw [T, H * D] decay logits (model type):
@@ -295,102 +420,253 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(const T* __restrict__ rp
                                                         RecurArgs a) {
   using L = Lay<R>;
   extern __shared__ __align__(16) float sm[];
-  const int D = a.D, Dv = a.Dv, H = a.H;
+  const int D = a.D, Dv = a.Dv, KS = a.KS, CW = a.CW, kTok = a.tok;
+  const int ROW = KS * L::SL;
   float* sr = sm;                       // [kTok][ROW]
-  float* sk = sr + kTok * L::ROW;       // [kTok][ROW]
-  float* sw = sk + kTok * L::ROW;       // [kTok][ROW]
-  float* sv = sw + kTok * L::ROW;       // [kTok][Dv]
-  float* so = sv + kTok * Dv;           // [kTok][Dv]
-  const int h = blockIdx.x, b = blockIdx.y;
+  float* sk = sr + kTok * ROW;          // [kTok][ROW]
+  float* sw = sk + kTok * ROW;          // [kTok][ROW]
+  float* sv = sw + kTok * ROW;          // [kTok][CW]
+  float* so = sv + kTok * CW;           // [kTok][CW]
+  float* part = so + kTok * CW;         // [2][kTokMax]
+  float* sinv = part + 2 * kTokMax;     // [kTokMax]
+  float* sc = sinv + kTokMax;           // [kTokMax]: sum_i r_i bonus_i k_i of the token
+  const int h = blockIdx.x / a.VT, vt = blockIdx.x % a.VT, b = blockIdx.y;
   int t0, n_new, start;
   portion(a.g, b, t0, n_new, start);
-  if (n_new <= 0) return;
+  if (n_new <= 0) return;               // the same for every CTA of the cluster
   const int slot = a.g.slots[b];
+  const int c0 = vt * CW, ncol = min(CW, Dv - c0);
   const int tid = threadIdx.x, j = tid / KS, ks = tid % KS;
-  for (int i = tid; i < 3 * kTok * L::ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
-  float S[R], U[R];
-  load_state<R>(S, a, slot, h, j, ks, start > 0);
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = ks * R + r;
-    U[r] = i < D ? bonus[h * D + i] : 0.f;
-  }
+  const bool valid = j < ncol;
+  for (int i = tid; i < 3 * kTok * ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
+  float S[R];
+  load_state<R>(S, a, slot, h, c0 + j, valid, ks, start > 0);
+  const int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
   __syncthreads();
-  for (int j0 = 0; j0 < n_new; j0 += kTok) {
-    const int n = min(kTok, n_new - j0);
-    for (int i = tid; i < n * D; i += blockDim.x) {
-      const int c = i / D, d = i - c * D;
-      const int64_t t = t0 + j0 + c;
-      const int col = h * D + d;
-      sr[c * L::ROW + L::at(d)] = to_f<T>(rp[t * r_stride + col]);
-      sk[c * L::ROW + L::at(d)] = to_f<T>(kp[t * k_stride + col]);
-      sw[c * L::ROW + L::at(d)] = expf(-expf(to_f<T>(wp[t * w_stride + col]) + w0[col]));
-    }
-    for (int i = tid; i < n * Dv; i += blockDim.x) {
-      const int c = i / Dv, d = i - c * Dv;
-      sv[c * Dv + d] = to_f<T>(vp[(int64_t)(t0 + j0 + c) * v_stride + h * Dv + d]);
-    }
-    __syncthreads();
-    for (int c = 0; c < n; ++c) {
-      const float4* r4 = reinterpret_cast<const float4*>(sr + c * L::ROW + ks * L::SL);
-      const float4* k4 = reinterpret_cast<const float4*>(sk + c * L::ROW + ks * L::SL);
-      const float4* w4 = reinterpret_cast<const float4*>(sw + c * L::ROW + ks * L::SL);
-      const float vj = j < Dv ? sv[c * Dv + j] : 0.f;
-      float o = 0.f;
+  // a stage's inputs are loaded into registers one stage ahead, so that their latency hides behind the tokens before
+  T pr_[kPF], pk_[kPF], pw_[kPF], pv_[kPFG], pg[kPFG];
+  auto prefetch = [&](int j0n) {
+    const int nn = min(kTok, n_new - j0n);
+    TileWalk w(D);
 #pragma unroll
-      for (int r = 0; r < R; r += 4) {
-        const float4 rr = r4[r / 4], kk = k4[r / 4], ww = w4[r / 4];
-        float kv;
-        kv = kk.x * vj; o = fmaf(rr.x, fmaf(U[r], kv, S[r]), o); S[r] = fmaf(ww.x, S[r], kv);
-        kv = kk.y * vj; o = fmaf(rr.y, fmaf(U[r + 1], kv, S[r + 1]), o); S[r + 1] = fmaf(ww.y, S[r + 1], kv);
-        kv = kk.z * vj; o = fmaf(rr.z, fmaf(U[r + 2], kv, S[r + 2]), o); S[r + 2] = fmaf(ww.z, S[r + 2], kv);
-        kv = kk.w * vj; o = fmaf(rr.w, fmaf(U[r + 3], kv, S[r + 3]), o); S[r + 3] = fmaf(ww.w, S[r + 3], kv);
+    for (int u = 0; u < kPF; ++u, w.next())
+      if (w.c < nn) {
+        const int64_t t = t0 + j0n + w.c;
+        const int col = h * D + w.d;
+        pr_[u] = rp[t * r_stride + col];
+        pk_[u] = kp[t * k_stride + col];
+        pw_[u] = wp[t * w_stride + col];
       }
-      o = slice_sum(o);
-      if (ks == 0 && j < Dv) so[c * Dv + j] = o;
+    TileWalk wv(ncol);
+#pragma unroll
+    for (int u = 0; u < kPFG; ++u, wv.next())
+      if (wv.c < nn) pv_[u] = vp[(int64_t)(t0 + j0n + wv.c) * v_stride + h * Dv + c0 + wv.d];
+  };
+  prefetch(0);
+  int stage = 0;
+  for (int j0 = 0; j0 < n_new; j0 += kTok, ++stage) {
+    const int n = min(kTok, n_new - j0);
+    {
+      TileWalk w(D);
+#pragma unroll
+      for (int u = 0; u < kPF; ++u, w.next())
+        if (w.c < n) {
+          sr[w.c * ROW + L::at(w.d)] = to_f<T>(pr_[u]);
+          sk[w.c * ROW + L::at(w.d)] = to_f<T>(pk_[u]);
+          sw[w.c * ROW + L::at(w.d)] = expf(-expf(to_f<T>(pw_[u]) + w0[h * D + w.d]));
+        }
+      for (; w.c < n; w.next()) {
+        const int64_t t = t0 + j0 + w.c;
+        const int col = h * D + w.d;
+        sr[w.c * ROW + L::at(w.d)] = to_f<T>(rp[t * r_stride + col]);
+        sk[w.c * ROW + L::at(w.d)] = to_f<T>(kp[t * k_stride + col]);
+        sw[w.c * ROW + L::at(w.d)] = expf(-expf(to_f<T>(wp[t * w_stride + col]) + w0[col]));
+      }
+      TileWalk wv(ncol);
+#pragma unroll
+      for (int u = 0; u < kPFG; ++u, wv.next())
+        if (wv.c < n) sv[wv.c * CW + wv.d] = to_f<T>(pv_[u]);
+      for (; wv.c < n; wv.next())
+        sv[wv.c * CW + wv.d] = to_f<T>(vp[(int64_t)(t0 + j0 + wv.c) * v_stride + h * Dv + c0 + wv.d]);
     }
     __syncthreads();
-    gated_unit_norm_rows<T>(a, so, h, t0 + j0, n);
+    if (j0 + kTok < n_new) prefetch(j0 + kTok);
+    prefetch_gates<T>(a, pg, h, c0, ncol, t0 + j0, n);
+    // the bonus acts on the token's own k v^T only:  (diag(bonus) k v^T)^T r = v * sum_i r_i bonus_i k_i, one number a token
+    for (int c = warp; c < n; c += warps) {
+      float acc = 0.f;
+      for (int d = lane; d < D; d += 32) acc += sr[c * ROW + L::at(d)] * bonus[h * D + d] * sk[c * ROW + L::at(d)];
+      acc = warp_sum(acc);
+      if (lane == 0) sc[c] = acc;
+    }
+    __syncthreads();
+    // One token: its r / k / w slices are in registers already (loaded while the token before ran); the next token's
+    // are requested first.  The read-out uses the state BEFORE the token's write; four partial sums keep its chain short.
+    auto step = [&](const float (&rc)[R], const float (&kc)[R], const float (&wc)[R], float (&rn)[R], float (&kn)[R],
+                    float (&wn)[R], int c, bool ahead) {
+      if (ahead && c + 1 < n) {
+        load_slice<R>(rn, sr + (c + 1) * ROW + ks * L::SL);
+        load_slice<R>(kn, sk + (c + 1) * ROW + ks * L::SL);
+        load_slice<R>(wn, sw + (c + 1) * ROW + ks * L::SL);
+      }
+      const float vj = valid ? sv[c * CW + j] : 0.f;
+      const float own = sc[c];
+      float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        o[r & 3] = fmaf(rc[r], S[r], o[r & 3]);
+        S[r] = fmaf(wc[r], S[r], kc[r] * vj);
+      }
+      const float os = slice_sum((o[0] + o[1]) + (o[2] + o[3]), KS);
+      if (ks == 0 && valid) so[c * CW + j] = fmaf(vj, own, os);
+    };
+    if constexpr (R <= 8) {
+      float ra[R], ka[R], wa[R], rb[R], kb[R], wb[R];
+      load_slice<R>(ra, sr + ks * L::SL);
+      load_slice<R>(ka, sk + ks * L::SL);
+      load_slice<R>(wa, sw + ks * L::SL);
+      for (int c = 0; c < n; c += 2) {
+        step(ra, ka, wa, rb, kb, wb, c, true);
+        if (c + 1 < n) step(rb, kb, wb, ra, ka, wa, c + 1, true);
+      }
+    } else {   // long slices: no registers to spare for the token ahead
+      float ra[R], ka[R], wa[R];
+      for (int c = 0; c < n; ++c) {
+        load_slice<R>(ra, sr + c * ROW + ks * L::SL);
+        load_slice<R>(ka, sk + c * ROW + ks * L::SL);
+        load_slice<R>(wa, sw + c * ROW + ks * L::SL);
+        step(ra, ka, wa, ra, ka, wa, c, false);
+      }
+    }
+    __syncthreads();
+    gated_unit_norm_rows<T>(a, so, part, sinv, stage, pg, h, c0, ncol, t0 + j0, n);
     __syncthreads();
   }
-  if (slot != a.reserved_slot) store_state<R>(S, a, slot, h, j, ks);
+  if (slot != a.reserved_slot) store_state<R>(S, a, slot, h, c0 + j, valid, ks);
+  if (a.VT > 1) cooperative_groups::this_cluster().sync();   // nobody leaves while its sums may still be read
 }
 
-inline int slice_rows(int D) {   // R: rows per slice, 8 .. 64 with 4 R >= D
-  int r = 8;
-  while (KS * r < D) r <<= 1;
-  return r;
+// How a (head, sequence) is laid out on CTAs and threads.
+struct RecurShape {
+  int R, KS, VT, CW, threads, tok;
+  size_t smem(int key_rows) const {   // key_rows: staged key-sized rows per token (2 delta, 3 wkv)
+    return sizeof(float) * ((size_t)key_rows * tok * KS * (R + 4) + (size_t)2 * tok * CW + tok * 4 + 4 * kTokMax);
+  }
+  // tokens per stage: as many as a portion has, up to kTokMax, within ~96 KB of shared memory (two CTAs still fit an SM)
+  void pick_tok(int max_new, int key_rows) {
+    tok = 1;
+    while (tok < kTokMax && tok < max_new) tok <<= 1;
+    while (tok > 1 && smem(key_rows) > 96 * 1024) tok >>= 1;
+  }
+};
+
+// VT: value columns go to 2 or 4 CTAs (a cluster) while a CTA keeps 32 columns or more and the step has few
+// (head, sequence) pairs for the SMs - and to as many as it takes (up to 8) for the CTA to fit 1024 threads;
+// R: the shortest register slice in {8, 16, 32} whose CTA fits 512 threads (128 registers a thread), else 1024;
+// KS: the power of two with KS * R >= D.  threads == 0: no layout (D or Dv too large).
+inline RecurShape recur_shape(int D, int Dv, int pairs, int max_new) {
+  RecurShape s{};
+  const int forced = test_options().recur_layout.load();
+  if (forced > 0) {   // tests and measurements: 100 * VT + R, taken when it fits
+    s.VT = forced / 100;
+    s.R = forced % 100;
+    if (s.VT >= 1 && s.VT <= 8 && Dv % s.VT == 0 && (s.R == 8 || s.R == 16 || s.R == 32)) {
+      s.CW = Dv / s.VT;
+      s.KS = 1;
+      while (s.KS * s.R < D) s.KS <<= 1;
+      if (s.KS <= kMaxSlices && s.CW * s.KS <= 1024) {
+        s.threads = cdiv(s.CW * s.KS, 32) * 32;
+        return s;
+      }
+    }
+    s = RecurShape{};
+  }
+  if (max_new == 1) {
+    // single tokens: the step is the state's trip through the registers, so many small CTAs (several per SM): columns
+    // in runs of 32 where they divide so, the longest slices
+    s.VT = 1;
+    while (s.VT < 8 && Dv % (2 * s.VT) == 0 && Dv / (2 * s.VT) >= 32) s.VT *= 2;
+    s.CW = Dv / s.VT;
+    for (int r = 32; r >= 8 && s.R == 0; r >>= 1) {
+      int ks = 1;
+      while (ks * r < D) ks <<= 1;
+      if (ks <= kMaxSlices && s.CW * ks <= 512) s.R = r, s.KS = ks;
+    }
+    if (s.R != 0) {
+      s.threads = cdiv(s.CW * s.KS, 32) * 32;
+      return s;
+    }
+    s = RecurShape{};
+  }
+  s.VT = 1;
+  while (s.VT < 4 && Dv % (2 * s.VT) == 0 && Dv / (2 * s.VT) >= 32 && (int64_t)pairs * s.VT < 2 * sm_count()) s.VT *= 2;
+  for (;; s.VT *= 2) {
+    s.CW = Dv / s.VT;
+    s.R = 0;
+    for (int limit = 512; limit <= 1024 && s.R == 0; limit *= 2)
+      for (int r = 8; r <= 32 && s.R == 0; r <<= 1) {
+        int ks = 1;
+        while (ks * r < D) ks <<= 1;
+        if (ks <= kMaxSlices && s.CW * ks <= limit) s.R = r, s.KS = ks;
+      }
+    if (s.R != 0) break;
+    if (s.VT >= 8 || Dv % (2 * s.VT) != 0) return s;   // threads stays 0
+  }
+  s.threads = cdiv(s.CW * s.KS, 32) * 32;
+  return s;
+}
+
+template <typename K, typename... Args>
+cudaError_t launch_clustered(K kern, dim3 grid, int threads, size_t smem, cudaStream_t st, int cluster, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cluster > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+template <int R>
+constexpr int max_recur_smem(int key_rows) {
+  // key rows of at most kMaxKeyDim numbers: KS <= kMaxKeyDim / R slices of R + 4 floats
+  (void)key_rows;
+  return 200 * 1024;   // a ceiling for every shape; a launch asks for what its stage size needs (pick_tok: <= ~96 KB)
 }
 
 template <typename T, int R, int MAXT>
-int launch_delta(dim3 grid, int threads, size_t smem, cudaStream_t st, const float* qkv, int64_t qkv_stride,
+int launch_delta(dim3 grid, const RecurShape& sh, cudaStream_t st, const float* qkv, int64_t qkv_stride,
                  const void* proj, int64_t proj_stride, int b_off, int a_off, const float* A_log, const float* dt_bias,
                  int G, const RecurArgs& a) {
-  // the attribute is set once per kernel: to what the largest value row needs, not to this launch's size
+  // the attribute is set once per kernel: to what the largest shape needs, not to this launch's size
   static std::atomic<uint64_t> attr{0};
-  constexpr int kMaxSmem = (int)sizeof(float) * (2 * kTok * KS * (R + 4) + 2 * kTok * kMaxValueDim + kTok * 4);
-  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)delta_rule_kernel<T, R, MAXT>, kMaxSmem, attr));
-  delta_rule_kernel<T, R, MAXT><<<grid, threads, smem, st>>>(qkv, qkv_stride, static_cast<const T*>(proj), proj_stride,
-                                                             b_off, a_off, A_log, dt_bias, G, a);
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)delta_rule_kernel<T, R, MAXT>, max_recur_smem<R>(2), attr));
+  CVLLM_CHECK_CUDA(launch_clustered(delta_rule_kernel<T, R, MAXT>, grid, sh.threads, sh.smem(2), st, sh.VT, qkv,
+                                    qkv_stride, static_cast<const T*>(proj), proj_stride, b_off, a_off, A_log, dt_bias,
+                                    G, a));
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
 }
 
 template <typename T, int R, int MAXT>
-int launch_wkv(dim3 grid, int threads, size_t smem, cudaStream_t st, const void* r, int64_t r_stride, const void* k,
+int launch_wkv(dim3 grid, const RecurShape& sh, cudaStream_t st, const void* r, int64_t r_stride, const void* k,
                int64_t k_stride, const void* v, int64_t v_stride, const void* w_raw, int64_t w_stride, const float* w0,
                const float* bonus, const RecurArgs& a) {
   static std::atomic<uint64_t> attr{0};
-  constexpr int kMaxSmem = (int)sizeof(float) * (3 * kTok * KS * (R + 4) + 2 * kTok * kMaxValueDim);
-  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)wkv_scan_kernel<T, R, MAXT>, kMaxSmem, attr));
-  wkv_scan_kernel<T, R, MAXT><<<grid, threads, smem, st>>>(static_cast<const T*>(r), r_stride, static_cast<const T*>(k),
-                                                           k_stride, static_cast<const T*>(v), v_stride,
-                                                           static_cast<const T*>(w_raw), w_stride, w0, bonus, a);
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)wkv_scan_kernel<T, R, MAXT>, max_recur_smem<R>(3), attr));
+  CVLLM_CHECK_CUDA(launch_clustered(wkv_scan_kernel<T, R, MAXT>, grid, sh.threads, sh.smem(3), st, sh.VT,
+                                    static_cast<const T*>(r), r_stride, static_cast<const T*>(k), k_stride,
+                                    static_cast<const T*>(v), v_stride, static_cast<const T*>(w_raw), w_stride, w0,
+                                    bonus, a));
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
 }
-
-inline int recur_threads(int Dv) { return cdiv(Dv * KS, 32) * 32; }
 
 }  // namespace
 }  // namespace cvllm
@@ -431,12 +707,11 @@ extern "C" int cvllm_token_shift_mix(const void* h, int64_t h_stride, const floa
 }
 
 // R rows per slice; CTAs of up to 512 threads get twice the registers of larger ones
-#define CVLLM_RECUR_BY_R(MACRO, T)                                              \
-  switch (R) {                                                                  \
-    case 8: return threads <= 512 ? MACRO(T, 8, 512) : MACRO(T, 8, 1024);       \
-    case 16: return threads <= 512 ? MACRO(T, 16, 512) : MACRO(T, 16, 1024);    \
-    case 32: return threads <= 512 ? MACRO(T, 32, 512) : MACRO(T, 32, 1024);    \
-    default: return threads <= 512 ? MACRO(T, 64, 512) : MACRO(T, 64, 1024);    \
+#define CVLLM_RECUR_BY_R(MACRO, T)                                                   \
+  switch (sh.R) {                                                                    \
+    case 8: return sh.threads <= 512 ? MACRO(T, 8, 512) : MACRO(T, 8, 1024);         \
+    case 16: return sh.threads <= 512 ? MACRO(T, 16, 512) : MACRO(T, 16, 1024);      \
+    default: return sh.threads <= 512 ? MACRO(T, 32, 512) : MACRO(T, 32, 1024);      \
   }
 
 extern "C" int cvllm_delta_rule(const float* qkv, int64_t qkv_stride, const void* proj, int64_t proj_stride, int b_off,
@@ -451,15 +726,16 @@ extern "C" int cvllm_delta_rule(const float* qkv, int64_t qkv_stride, const void
   CVLLM_CHECK_ARG(qkv && proj && A_log && dt_bias && state && gate && norm_w && batch_mapping && out &&
                   recur_dtype_ok(dtype));
   CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
-  CVLLM_CHECK_SUPPORTED(D <= 256 && Dv <= kMaxValueDim && H <= 65535 && B <= 65535);
+  CVLLM_CHECK_SUPPORTED(D <= kMaxKeyDim && Dv <= kMaxValueDim && H <= 65535 && B <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
-  const int R = slice_rows(D), threads = recur_threads(Dv);
-  const size_t smem = sizeof(float) * ((size_t)2 * kTok * KS * (R + 4) + (size_t)2 * kTok * Dv + kTok * 4);
+  RecurShape sh = recur_shape(D, Dv, H * B, max_new);
+  sh.pick_tok(max_new, 2);
+  CVLLM_CHECK_SUPPORTED(sh.threads > 0 && sh.threads <= 1024 && (int64_t)H * sh.VT <= 2147483647);
   RecurArgs a{{cu_seqlens_q, seq_start, positions, batch_mapping}, state, gate, gate_stride, gate_off, norm_w,
-              norm_head_stride, eps, out, out_stride, H, D, Dv, reserved_slot};
-  const dim3 grid(H, B);
+              norm_head_stride, eps, out, out_stride, H, D, Dv, reserved_slot, sh.KS, sh.VT, sh.CW, sh.tok};
+  const dim3 grid(H * sh.VT, B);
 #define CVLLM_DELTA(T, RR, MT) \
-  launch_delta<T, RR, MT>(grid, threads, smem, st, qkv, qkv_stride, proj, proj_stride, b_off, a_off, A_log, dt_bias, G, a)
+  launch_delta<T, RR, MT>(grid, sh, st, qkv, qkv_stride, proj, proj_stride, b_off, a_off, A_log, dt_bias, G, a)
   if (dtype == CVLLM_BF16) { CVLLM_RECUR_BY_R(CVLLM_DELTA, __nv_bfloat16) }
   CVLLM_RECUR_BY_R(CVLLM_DELTA, float)
 #undef CVLLM_DELTA
@@ -480,13 +756,14 @@ extern "C" int cvllm_wkv_scan(const void* r, int64_t r_stride, const void* k, in
   CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
   CVLLM_CHECK_SUPPORTED(D <= kMaxValueDim && H <= 65535 && B <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
-  const int R = slice_rows(D), threads = recur_threads(D);
-  const size_t smem = sizeof(float) * ((size_t)3 * kTok * KS * (R + 4) + (size_t)2 * kTok * D);
+  RecurShape sh = recur_shape(D, D, H * B, max_new);
+  sh.pick_tok(max_new, 3);
+  CVLLM_CHECK_SUPPORTED(sh.threads > 0 && sh.threads <= 1024 && (int64_t)H * sh.VT <= 2147483647);
   RecurArgs a{{cu_seqlens_q, seq_start, positions, batch_mapping}, state, gate, gate_stride, gate_off, norm_w,
-              norm_head_stride, eps, out, out_stride, H, D, D, reserved_slot};
-  const dim3 grid(H, B);
+              norm_head_stride, eps, out, out_stride, H, D, D, reserved_slot, sh.KS, sh.VT, sh.CW, sh.tok};
+  const dim3 grid(H * sh.VT, B);
 #define CVLLM_WKV(T, RR, MT) \
-  launch_wkv<T, RR, MT>(grid, threads, smem, st, r, r_stride, k, k_stride, v, v_stride, w_raw, w_stride, w0, bonus, a)
+  launch_wkv<T, RR, MT>(grid, sh, st, r, r_stride, k, k_stride, v, v_stride, w_raw, w_stride, w0, bonus, a)
   if (dtype == CVLLM_BF16) { CVLLM_RECUR_BY_R(CVLLM_WKV, __nv_bfloat16) }
   CVLLM_RECUR_BY_R(CVLLM_WKV, float)
 #undef CVLLM_WKV

@@ -110,6 +110,7 @@ extern "C" int cvllm_set_test_option(const char* name, double value) {
   else if (!strcmp(name, "grs_rows_per_round")) o.grs_rows_per_round = (int)value;
   else if (!strcmp(name, "bias_attn_fma")) o.bias_attn_fma = (int)value;
   else if (!strcmp(name, "ssm_segment")) o.ssm_segment = (int)value;
+  else if (!strcmp(name, "recur_layout")) o.recur_layout = (int)value;
   else {
     cvllm::set_last_error("unknown test option");
     return CVLLM_E_ARG;

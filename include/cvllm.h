@@ -587,7 +587,8 @@ int cvllm_gated_group_norm(const float* y, int64_t y_stride, const void* z, int6
  * Mixers with a [key, value] matrix state per head (csrc/recurrent.cu).  Step geometry as for the state-space mixer.
  * Both recurrences end, inside the kernel, with each head's unit norm, a weight and a gate:
  *   out[t, h * Dv + j] = o / sqrt(mean_j(o^2) + eps) * norm_w[h * norm_head_stride + j] * silu(gate[t, gate_off + h * Dv + j])
- * (norm_head_stride 0: one weight vector shared by the heads).  state [slots, H, D, Dv] fp32.  D, Dv <= 256.
+ * (norm_head_stride 0: one weight vector shared by the heads).  state [slots, H, Dv, D] fp32 (the key rows of a value
+ * column are contiguous).  D, Dv <= 256.
  * --------------------------------------------------------------------- */
 
 /* out[s, t, :] = h[t] + (h[t - 1] - h[t]) * mu[s, :] for s < S (out [S, total_tokens, W], model type, mu fp32 [S, W]);

@@ -293,6 +293,25 @@ def test_state_far_back_reaches_the_last_token(kind):
         assert rel_err(run_in_portions(r, toks, sizes), want) < TOL["float32"], sizes
 
 
+@pytest.mark.parametrize("layout", [108, 208, 216, 416, 432, 832])
+def test_recurrent_layouts_give_the_same_numbers(layout):
+    """The matrix-state kernels spread a head's value columns over a cluster of 1 to 8 CTAs and its key rows over
+    register slices of 8 to 32 numbers; whatever the layout, the logits are the oracle's (portions and decoding)."""
+    from compactor_vllm import _native as N
+    from oracle import fafelix as O
+
+    cfg = model_cfg([(delta(2, 1, 48, 64, 3), None), (wkv(2, 64), dense(24))], width=40, loop=(0, 2, 2))
+    r = make_runner(cfg, "float32", pages=12, page_size=16)
+    toks = tokens(90, 83, 12)
+    want = O.forward(oracle_model(r.model), toks)
+    N.set_test_option("recur_layout", layout)
+    try:
+        for sizes in ([90], [70, 1, 1, 3], [33]):
+            assert rel_err(run_in_portions(r, toks, sizes), want) < TOL["float32"], sizes
+    finally:
+        N.set_test_option("recur_layout", 0)
+
+
 # ---------------------------------------------------------------------------------- batches, pages and slots reused
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_mixed_batches_equal_each_request_alone(dtype):
