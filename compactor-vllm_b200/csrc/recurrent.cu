@@ -235,25 +235,46 @@ __device__ __forceinline__ void gated_unit_norm_rows(const RecurArgs& a, const f
     emit(w.c, w.d, to_f<T>(gate[(int64_t)(tok0 + w.c) * a.gate_stride + a.gate_off + h * a.Dv + c0 + w.d]));
 }
 
+// State of (slot, head): [Dv, D] fp32, the key rows of a value column contiguous - a thread's slice is R consecutive
+// numbers, moved as 16-byte pieces when the key size allows.
 template <int R>
 __device__ __forceinline__ void load_state(float (&S)[R], const RecurArgs& a, int slot, int h, int col, bool valid,
                                            int ks, bool from_pool) {
-  const float* src = a.state + ((int64_t)slot * a.H + h) * a.D * a.Dv;
+  const float* src = a.state + (((int64_t)slot * a.H + h) * a.Dv + col) * a.D;
+  const bool on = from_pool && valid;
+  if ((a.D & 3) == 0) {
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = ks * R + r;
-    S[r] = (from_pool && valid && i < a.D) ? src[(int64_t)col * a.D + i] : 0.f;
+    for (int r = 0; r < R; r += 4) {
+      const int i = ks * R + r;
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (on && i < a.D) t = *reinterpret_cast<const float4*>(src + i);
+      S[r] = t.x; S[r + 1] = t.y; S[r + 2] = t.z; S[r + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = ks * R + r;
+      S[r] = (on && i < a.D) ? src[i] : 0.f;
+    }
   }
 }
 
 template <int R>
 __device__ __forceinline__ void store_state(const float (&S)[R], const RecurArgs& a, int slot, int h, int col,
                                             bool valid, int ks) {
-  float* dst = a.state + ((int64_t)slot * a.H + h) * a.D * a.Dv;
+  float* dst = a.state + (((int64_t)slot * a.H + h) * a.Dv + col) * a.D;
+  if ((a.D & 3) == 0) {
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = ks * R + r;
-    if (valid && i < a.D) dst[(int64_t)col * a.D + i] = S[r];
+    for (int r = 0; r < R; r += 4) {
+      const int i = ks * R + r;
+      if (valid && i < a.D) *reinterpret_cast<float4*>(dst + i) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = ks * R + r;
+      if (valid && i < a.D) dst[i] = S[r];
+    }
   }
 }
 
