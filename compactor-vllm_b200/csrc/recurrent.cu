@@ -126,19 +126,43 @@ struct Lay {
   __device__ static __forceinline__ int at(int i) { return (i / R) * SL + (i % R); }
 };
 
+// sums over the KS lanes (a power of two, neighbours in the warp) that hold the slices of one value column; straight-line
+// code per slice count, the two sums of slice_sum2 interleaved
 __device__ __forceinline__ float slice_sum(float v, int KS) {
-  for (int o = KS >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  switch (KS) {
+    case 32: v += __shfl_xor_sync(0xffffffffu, v, 16); [[fallthrough]];
+    case 16: v += __shfl_xor_sync(0xffffffffu, v, 8); [[fallthrough]];
+    case 8: v += __shfl_xor_sync(0xffffffffu, v, 4); [[fallthrough]];
+    case 4: v += __shfl_xor_sync(0xffffffffu, v, 2); [[fallthrough]];
+    case 2: v += __shfl_xor_sync(0xffffffffu, v, 1); [[fallthrough]];
+    default: break;
+  }
   return v;
 }
 
-// a thread's slice (R numbers) of a staged key-sized row, as 16-byte loads
+__device__ __forceinline__ void slice_sum2(float& a, float& b, int KS) {
+#define CVLLM_STEP(o) a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o)
+  switch (KS) {
+    case 32: CVLLM_STEP(16); [[fallthrough]];
+    case 16: CVLLM_STEP(8); [[fallthrough]];
+    case 8: CVLLM_STEP(4); [[fallthrough]];
+    case 4: CVLLM_STEP(2); [[fallthrough]];
+    case 2: CVLLM_STEP(1); [[fallthrough]];
+    default: break;
+  }
+#undef CVLLM_STEP
+}
+
+// a thread's slice (R numbers) of a staged key-sized row, as 16-byte loads into pairs (the arithmetic on the slices is
+// packed: one fp32x2 instruction per two rows, each half an ordinary IEEE operation)
 template <int R>
-__device__ __forceinline__ void load_slice(float (&dst)[R], const float* row_slice) {
+__device__ __forceinline__ void load_slice(float2 (&dst)[R / 2], const float* row_slice) {
   const float4* p = reinterpret_cast<const float4*>(row_slice);
 #pragma unroll
   for (int r = 0; r < R; r += 4) {
     const float4 t = p[r / 4];
-    dst[r] = t.x; dst[r + 1] = t.y; dst[r + 2] = t.z; dst[r + 3] = t.w;
+    dst[r / 2] = make_float2(t.x, t.y);
+    dst[r / 2 + 1] = make_float2(t.z, t.w);
   }
 }
 
@@ -238,7 +262,7 @@ __device__ __forceinline__ void gated_unit_norm_rows(const RecurArgs& a, const f
 // State of (slot, head): [Dv, D] fp32, the key rows of a value column contiguous - a thread's slice is R consecutive
 // numbers, moved as 16-byte pieces when the key size allows.
 template <int R>
-__device__ __forceinline__ void load_state(float (&S)[R], const RecurArgs& a, int slot, int h, int col, bool valid,
+__device__ __forceinline__ void load_state(float2 (&S)[R / 2], const RecurArgs& a, int slot, int h, int col, bool valid,
                                            int ks, bool from_pool) {
   const float* src = a.state + (((int64_t)slot * a.H + h) * a.Dv + col) * a.D;
   const bool on = from_pool && valid;
@@ -248,32 +272,35 @@ __device__ __forceinline__ void load_state(float (&S)[R], const RecurArgs& a, in
       const int i = ks * R + r;
       float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
       if (on && i < a.D) t = *reinterpret_cast<const float4*>(src + i);
-      S[r] = t.x; S[r + 1] = t.y; S[r + 2] = t.z; S[r + 3] = t.w;
+      S[r / 2] = make_float2(t.x, t.y);
+      S[r / 2 + 1] = make_float2(t.z, t.w);
     }
   } else {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
+    for (int r = 0; r < R; r += 2) {
       const int i = ks * R + r;
-      S[r] = (on && i < a.D) ? src[i] : 0.f;
+      S[r / 2] = make_float2((on && i < a.D) ? src[i] : 0.f, (on && i + 1 < a.D) ? src[i + 1] : 0.f);
     }
   }
 }
 
 template <int R>
-__device__ __forceinline__ void store_state(const float (&S)[R], const RecurArgs& a, int slot, int h, int col,
+__device__ __forceinline__ void store_state(const float2 (&S)[R / 2], const RecurArgs& a, int slot, int h, int col,
                                             bool valid, int ks) {
   float* dst = a.state + (((int64_t)slot * a.H + h) * a.Dv + col) * a.D;
   if ((a.D & 3) == 0) {
 #pragma unroll
     for (int r = 0; r < R; r += 4) {
       const int i = ks * R + r;
-      if (valid && i < a.D) *reinterpret_cast<float4*>(dst + i) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+      if (valid && i < a.D)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(S[r / 2].x, S[r / 2].y, S[r / 2 + 1].x, S[r / 2 + 1].y);
     }
   } else {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
+    for (int r = 0; r < R; r += 2) {
       const int i = ks * R + r;
-      if (valid && i < a.D) dst[i] = S[r];
+      if (valid && i < a.D) dst[i] = S[r / 2].x;
+      if (valid && i + 1 < a.D) dst[i + 1] = S[r / 2].y;
     }
   }
 }
@@ -310,7 +337,7 @@ __global__ void __launch_bounds__(MAXT) delta_rule_kernel(const float* __restric
   const bool valid = j < ncol;
   const int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
   for (int i = tid; i < 2 * kTok * ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
-  float S[R];
+  float2 S[R / 2];
   load_state<R>(S, a, slot, h, c0 + j, valid, ks, start > 0);
   const float neg_a = -expf(A_log[h]), dtb = dt_bias[h];
   const float q_scale = rsqrtf((float)D);
@@ -386,28 +413,30 @@ __global__ void __launch_bounds__(MAXT) delta_rule_kernel(const float* __restric
     __syncthreads();
     // One token: its key / query slices are in registers already (loaded while the token before ran); the next token's
     // are requested first.  Four partial sums per dot product keep the multiply-add chains short.
-    auto step = [&](const float (&kc)[R], const float (&qc)[R], float (&kn)[R], float (&qn)[R], int c, bool ahead) {
+    auto step = [&](const float2 (&kc)[R / 2], const float2 (&qc)[R / 2], float2 (&kn)[R / 2], float2 (&qn)[R / 2], int c,
+                    bool ahead) {
       if (ahead && c + 1 < n) {
         load_slice<R>(kn, sk + (c + 1) * ROW + ks * L::SL);
         load_slice<R>(qn, sq + (c + 1) * ROW + ks * L::SL);
       }
       const float gd = sc[c * 4 + 0], beta = sc[c * 4 + 1], kq_dot = sc[c * 4 + 2];
       const float vj = valid ? sv[c * CW + j] : 0.f;
-      float dk[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};
+      float2 dk[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)}, dq[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        dk[r & 3] = fmaf(S[r], kc[r], dk[r & 3]);
-        dq[r & 3] = fmaf(S[r], qc[r], dq[r & 3]);
+      for (int r = 0; r < R / 2; ++r) {
+        dk[r & 1] = __ffma2_rn(S[r], kc[r], dk[r & 1]);
+        dq[r & 1] = __ffma2_rn(S[r], qc[r], dq[r & 1]);
       }
-      const float dks = slice_sum((dk[0] + dk[1]) + (dk[2] + dk[3]), KS);
-      const float dqs = slice_sum((dq[0] + dq[1]) + (dq[2] + dq[3]), KS);
+      float dks = (dk[0].x + dk[0].y) + (dk[1].x + dk[1].y), dqs = (dq[0].x + dq[0].y) + (dq[1].x + dq[1].y);
+      slice_sum2(dks, dqs, KS);
       const float u = beta * (vj - gd * dks);
       if (ks == 0 && valid) so[c * CW + j] = fmaf(kq_dot, u, gd * dqs);
+      const float2 u2 = make_float2(u, u), g2 = make_float2(gd, gd);
 #pragma unroll
-      for (int r = 0; r < R; ++r) S[r] = fmaf(kc[r], u, gd * S[r]);
+      for (int r = 0; r < R / 2; ++r) S[r] = __ffma2_rn(kc[r], u2, __fmul2_rn(g2, S[r]));
     };
     if constexpr (R <= 16) {
-      float ka[R], qa[R], kb[R], qb[R];
+      float2 ka[R / 2], qa[R / 2], kb[R / 2], qb[R / 2];
       load_slice<R>(ka, sk + ks * L::SL);
       load_slice<R>(qa, sq + ks * L::SL);
       for (int c = 0; c < n; c += 2) {
@@ -415,7 +444,7 @@ __global__ void __launch_bounds__(MAXT) delta_rule_kernel(const float* __restric
         if (c + 1 < n) step(kb, qb, ka, qa, c + 1, true);
       }
     } else {   // long slices: no registers to spare for the token ahead
-      float ka[R], qa[R];
+      float2 ka[R / 2], qa[R / 2];
       for (int c = 0; c < n; ++c) {
         load_slice<R>(ka, sk + c * ROW + ks * L::SL);
         load_slice<R>(qa, sq + c * ROW + ks * L::SL);
@@ -460,7 +489,7 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(const T* __restrict__ rp
   const int tid = threadIdx.x, j = tid / KS, ks = tid % KS;
   const bool valid = j < ncol;
   for (int i = tid; i < 3 * kTok * ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
-  float S[R];
+  float2 S[R / 2];
   load_state<R>(S, a, slot, h, c0 + j, valid, ks, start > 0);
   const int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
   __syncthreads();
@@ -523,8 +552,8 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(const T* __restrict__ rp
     __syncthreads();
     // One token: its r / k / w slices are in registers already (loaded while the token before ran); the next token's
     // are requested first.  The read-out uses the state BEFORE the token's write; four partial sums keep its chain short.
-    auto step = [&](const float (&rc)[R], const float (&kc)[R], const float (&wc)[R], float (&rn)[R], float (&kn)[R],
-                    float (&wn)[R], int c, bool ahead) {
+    auto step = [&](const float2 (&rc)[R / 2], const float2 (&kc)[R / 2], const float2 (&wc)[R / 2], float2 (&rn)[R / 2],
+                    float2 (&kn)[R / 2], float2 (&wn)[R / 2], int c, bool ahead) {
       if (ahead && c + 1 < n) {
         load_slice<R>(rn, sr + (c + 1) * ROW + ks * L::SL);
         load_slice<R>(kn, sk + (c + 1) * ROW + ks * L::SL);
@@ -532,17 +561,19 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(const T* __restrict__ rp
       }
       const float vj = valid ? sv[c * CW + j] : 0.f;
       const float own = sc[c];
-      float o[4] = {0.f, 0.f, 0.f, 0.f};
+      float2 o[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        o[r & 3] = fmaf(rc[r], S[r], o[r & 3]);
-        S[r] = fmaf(wc[r], S[r], kc[r] * vj);
+      for (int r = 0; r < R / 2; ++r) {
+        o[r & 1].x = fmaf(rc[r].x, S[r].x, o[r & 1].x);
+        o[r & 1].y = fmaf(rc[r].y, S[r].y, o[r & 1].y);
+        S[r].x = fmaf(wc[r].x, S[r].x, kc[r].x * vj);
+        S[r].y = fmaf(wc[r].y, S[r].y, kc[r].y * vj);
       }
-      const float os = slice_sum((o[0] + o[1]) + (o[2] + o[3]), KS);
+      const float os = slice_sum((o[0].x + o[0].y) + (o[1].x + o[1].y), KS);
       if (ks == 0 && valid) so[c * CW + j] = fmaf(vj, own, os);
     };
     if constexpr (R <= 8) {
-      float ra[R], ka[R], wa[R], rb[R], kb[R], wb[R];
+      float2 ra[R / 2], ka[R / 2], wa[R / 2], rb[R / 2], kb[R / 2], wb[R / 2];
       load_slice<R>(ra, sr + ks * L::SL);
       load_slice<R>(ka, sk + ks * L::SL);
       load_slice<R>(wa, sw + ks * L::SL);
@@ -551,7 +582,7 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(const T* __restrict__ rp
         if (c + 1 < n) step(rb, kb, wb, ra, ka, wa, c + 1, true);
       }
     } else {   // long slices: no registers to spare for the token ahead
-      float ra[R], ka[R], wa[R];
+      float2 ra[R / 2], ka[R / 2], wa[R / 2];
       for (int c = 0; c < n; ++c) {
         load_slice<R>(ra, sr + c * ROW + ks * L::SL);
         load_slice<R>(ka, sk + c * ROW + ks * L::SL);
@@ -573,7 +604,7 @@ struct RecurShape {
   size_t smem(int key_rows) const {   // key_rows: staged key-sized rows per token (2 delta, 3 wkv)
     return sizeof(float) * ((size_t)key_rows * tok * KS * (R + 4) + (size_t)2 * tok * CW + tok * 4 + 4 * kTokMax);
   }
-  // tokens per stage: as many as a portion has, up to kTokMax, within ~96 KB of shared memory (two CTAs still fit an SM)
+  // tokens per stage: as many as a portion has, up to kTokMax, within 96 KB of shared memory (longer stages outrun the registers that load a stage ahead: 64 tokens measured 2-4 % slower than 32 at heads of 128 x 128 and 64 x 64)
   void pick_tok(int max_new, int key_rows) {
     tok = 1;
     while (tok < kTokMax && tok < max_new) tok <<= 1;
@@ -581,8 +612,9 @@ struct RecurShape {
   }
 };
 
-// VT: value columns go to 2 or 4 CTAs (a cluster) while a CTA keeps 32 columns or more and the step has few
-// (head, sequence) pairs for the SMs - and to as many as it takes (up to 8) for the CTA to fit 1024 threads;
+// VT: value columns go to 2 or 4 CTAs (a cluster) while a CTA keeps 32 columns or more and 512 threads (fewer warps
+// per CTA lost more than the extra CTAs won: wkv 64 x 64, 2.28 against 2.06 ms) and the step has few (head, sequence)
+// pairs for the SMs - and to as many as it takes (up to 8) for the CTA to fit 1024 threads;
 // R: the shortest register slice in {8, 16, 32} whose CTA fits 512 threads (128 registers a thread), else 1024;
 // KS: the power of two with KS * R >= D.  threads == 0: no layout (D or Dv too large).
 inline RecurShape recur_shape(int D, int Dv, int pairs, int max_new) {
@@ -619,8 +651,12 @@ inline RecurShape recur_shape(int D, int Dv, int pairs, int max_new) {
     }
     s = RecurShape{};
   }
+  int ks8 = 1;   // slices of 8 rows
+  while (ks8 * 8 < D) ks8 <<= 1;
   s.VT = 1;
-  while (s.VT < 4 && Dv % (2 * s.VT) == 0 && Dv / (2 * s.VT) >= 32 && (int64_t)pairs * s.VT < 2 * sm_count()) s.VT *= 2;
+  while (s.VT < 4 && Dv % (2 * s.VT) == 0 && Dv / (2 * s.VT) >= 32 && (Dv / (2 * s.VT)) * ks8 >= 512 &&
+         (int64_t)pairs * s.VT < 2 * sm_count())
+    s.VT *= 2;
   for (;; s.VT *= 2) {
     s.CW = Dv / s.VT;
     s.R = 0;
@@ -658,7 +694,7 @@ template <int R>
 constexpr int max_recur_smem(int key_rows) {
   // key rows of at most kMaxKeyDim numbers: KS <= kMaxKeyDim / R slices of R + 4 floats
   (void)key_rows;
-  return 200 * 1024;   // a ceiling for every shape; a launch asks for what its stage size needs (pick_tok: <= ~96 KB)
+  return 200 * 1024;   // a ceiling for every shape; a launch asks for what its stage size needs (pick_tok: <= 96 KB)
 }
 
 template <typename T, int R, int MAXT>
