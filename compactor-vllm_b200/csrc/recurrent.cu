@@ -15,7 +15,7 @@
 // replays).  A portion that starts at position 0 starts from a zero state whatever the slot holds.  States, decays,
 // gates of the recurrence, norms and the outputs before the final rounding are fp32.
 //
-// Recurrence kernels: a cluster of up to four CTAs per (head, sequence), the state in registers; see below.
+// Recurrence kernels: a cluster of one to eight CTAs per (head, sequence), the state in registers; see below.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
