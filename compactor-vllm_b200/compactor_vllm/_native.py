@@ -105,6 +105,22 @@ _SIGNATURES = {
     "cvllm_token_shift_mix": (_i, [_p, _i64, _p, _i, _i, _p, _p, _p, _p, _p, _i, _i, _p, _i64, _i, _i, _p]),
     "cvllm_delta_rule": (_i, [_p, _i64, _p, _i64, _i, _i, _p, _p, _p, _p, _i64, _i, _p, _i, _f, _p, _p, _p, _p, _i, _i,
                               _p, _i64, _i, _i, _i, _i, _i, _i, _p]),
+    "cvllm_bias_attn_varlen_dist": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _p, _i, _i, _p, _f, _p,
+                                         _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i64, _i, _p]),
+    "cvllm_bias_attn_decode_dist": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _i, _i, _p, _i, _i, _p, _f, _p,
+                                         _i, _i, _i, _i, _i, _i, _i, _p, _sz, _i64, _i, _p]),
+    "cvllm_general_delta": (_i, [_p, _i64, _i, _i, _i, _i, _p, _i64, _p, _f, _p, _i, _i, _p, _i, _f, _p, _p, _p, _p,
+                                 _i, _i, _p, _i64, _i, _i, _i, _i, _p]),
+    "cvllm_matrix_memory": (_i, [_p, _i64, _i, _i, _i, _i, _i, _f, _f, _p, _p, _p, _i, _i, _p, _i, _f, _p, _p, _p, _p,
+                                 _i, _i, _p, _i64, _i, _i, _i, _i, _i, _p]),
+    "cvllm_causal_conv_mode": (_i, [_p, _i64, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i64, _i, _i, _i, _p]),
+    "cvllm_selective_scan": (_i, [_p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _p, _p, _p, _i64, _i, _p, _p, _p, _p, _p,
+                                  _i, _i, _p, _i64, _i, _i, _i, _i, _p]),
+    "cvllm_gated_residual_norm": (_i, [_p, _i64, _i, _p, _i64, _i, _p, _i64, _p, _p, _i64, _i, _i, _i, _f, _p]),
+    "cvllm_dual_norm_blend": (_i, [_p, _i64, _p, _p, _i64, _p, _p, _i64, _i, _i, _f, _f, _i, _p]),
+    "cvllm_unary_act": (_i, [_p, _i64, _p, _i64, _i64, _i, _i, _i, _p]),
+    "cvllm_softcap": (_i, [_p, _i64, _p, _i64, _i64, _i, _f, _i, _p]),
+    "cvllm_scaled_rows": (_i, [_p, _i64, _p, _p, _i, _p, _i64, _i, _i, _p]),
     "cvllm_wkv_scan": (_i, [_p, _i64, _p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _i64, _i, _p, _i, _f, _p, _p, _p, _p,
                             _i, _i, _p, _i64, _i, _i, _i, _i, _p]),
 }

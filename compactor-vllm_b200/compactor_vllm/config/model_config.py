@@ -431,7 +431,192 @@ class FafelixConfig:
         return max([a.dim for a in self._attn()] or [1])
 
 
-ARCHITECTURES = {"Movolorn": MovolornConfig, "Batasun": BatasunConfig, "Fafelix": FafelixConfig}
+@dataclass
+class GeneralDeltaConfig:
+    """General delta rule (layers/recurrent.py): `heads` heads of `dim` key and value channels, a decay and a removal
+    rate per key channel.  `decay_rank` (the inner size of the decay's two-step projection) is not part of
+    config.json: a checkpoint's tensors give it; the default serves synthetic weights."""
+    heads: int
+    dim: int
+    decay_rank: int = 16
+
+    @classmethod
+    def from_json(cls, m: dict) -> "GeneralDeltaConfig":
+        return cls(heads=int(m["heads"]), dim=int(m["dim"]), decay_rank=int(m.get("decay_rank", 16)))
+
+
+@dataclass
+class WindowAttentionConfig:
+    """Grouped-query attention without rotation: a sliding window of `window` positions (0 = none), a learned bias per
+    distance bucket (a table of `bias_rows` rows per head - a checkpoint's tensor gives the count -, exact distances
+    below half of it, logarithmic buckets up to `bias_max`) and a learned softmax sink per head."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int
+    bias_max: int
+    bias_rows: int = 16
+
+    @classmethod
+    def from_json(cls, m: dict) -> "WindowAttentionConfig":
+        dim = int(m["dim"])
+        c = cls(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=dim,
+                vdim=int(m.get("vdim", dim)), scale=float(m.get("scale", dim ** -0.5)),
+                window=int((m.get("mask") or {}).get("size", 0) or 0), bias_max=int(m["bias_max"]),
+                bias_rows=int(m.get("bias_rows", 16)))
+        if c.heads % c.kv_heads or c.window < 0 or c.bias_max < 2:
+            raise ValueError(f"attention: {c.heads} heads / {c.kv_heads} kv heads, window {c.window}, bias_max {c.bias_max}")
+        return c
+
+
+@dataclass
+class MatrixMemoryConfig:
+    """Matrix memory with exponential gates (layers/recurrent.py): `heads` heads of `dim` key and `vdim` value
+    channels; the log gates are capped at +-`gate_cap` by a tanh."""
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+
+    @classmethod
+    def from_json(cls, m: dict) -> "MatrixMemoryConfig":
+        dim = int(m["dim"])
+        c = cls(heads=int(m["heads"]), dim=dim, vdim=int(m.get("vdim", dim)), gate_cap=float(m["gate_cap"]))
+        if c.gate_cap <= 0:
+            raise ValueError(f"matrix memory: gate_cap {c.gate_cap}")
+        return c
+
+
+@dataclass
+class ParallelMixerConfig:
+    """Two mixers side by side on one input: windowed attention (`left`) and a matrix memory (`right`)."""
+    left: WindowAttentionConfig
+    right: MatrixMemoryConfig
+
+    @classmethod
+    def from_json(cls, m: dict) -> "ParallelMixerConfig":
+        return cls(WindowAttentionConfig.from_json(m["left"]), MatrixMemoryConfig.from_json(m["right"]))
+
+
+@dataclass
+class SelectiveScanConfig:
+    """State-space mixer with a decay per (channel, state channel) (layers/ssm.py): `inner` channels with `state` state
+    channels each, step sizes through a projection of rank `dt_rank`, a causal convolution of `conv` taps in front."""
+    inner: int
+    state: int
+    dt_rank: int
+    conv: int
+
+    @classmethod
+    def from_json(cls, m: dict) -> "SelectiveScanConfig":
+        c = cls(inner=int(m["inner"]), state=int(m["state"]), dt_rank=int(m["dt_rank"]), conv=int(m.get("conv", 4)))
+        if min(c.inner, c.state, c.dt_rank, c.conv) < 1:
+            raise ValueError(f"selective scan: {c}")
+        return c
+
+
+@dataclass
+class ScaledMoEConfig:
+    """kind "dense": down(relu(up h + b)^2) + b.  kind "moe": `experts` silu-gated experts of size `ff`, `top` per token
+    by the largest sigmoid(router logit); the weight (that sigmoid, not renormalized) multiplies the expert's INPUT; a
+    shared expert of size `shared_ff` (0 = none) is added, scaled by the sigmoid of one logit per token."""
+    kind: str
+    ff: int
+    experts: int = 0
+    top: int = 0
+    shared_ff: int = 0
+
+    @classmethod
+    def from_json(cls, m: Optional[dict]) -> Optional["ScaledMoEConfig"]:
+        if m is None:
+            return None
+        kind = m.get("kind", "dense")
+        if kind == "dense":
+            return cls(kind="dense", ff=int(m["ff"]))
+        if kind != "moe":
+            raise ValueError(f"unknown feed-forward kind {kind!r}")
+        shared = m.get("shared") or {}
+        c = cls(kind="moe", ff=int(m["expert"]["ff"]), experts=int(m["router"]["experts"]), top=int(m["router"]["top"]),
+                shared_ff=int(shared.get("ff", 0) or 0))
+        if not 1 <= c.top <= c.experts:
+            raise ValueError(f"mixture of experts: top {c.top} of {c.experts}")
+        return c
+
+
+@dataclass
+class NununexLayerConfig:
+    mixer_type: str                     # "general_delta" | "parallel" | "mamba1"
+    mixer: Any                          # GeneralDeltaConfig | ParallelMixerConfig | SelectiveScanConfig
+    mlp: Optional[ScaledMoEConfig]
+
+
+@dataclass
+class NununexConfig:
+    """config.json of a Nununex model: `vocab`, `width`, `norm.eps`, `canon.taps`, `logit_softcap`,
+    `embedding.bigram` (`buckets`, `mul_prev`, `mul_cur`), `layers` (each with `type`, `mixer`, `mlp`).  Every sublayer
+    is x += sigmoid(W_rg h + b) * sublayer(h + causal_conv(h)) with h = rms_norm(x); the logits pass a tanh cap."""
+    vocab_size: int
+    hidden_size: int
+    rms_norm_eps: float
+    canon_taps: int
+    logit_softcap: float                # 0 = none
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    layers: List[NununexLayerConfig]
+    torch_dtype: Any = torch.bfloat16
+    max_position_embeddings: int = 1 << 30      # positions enter through distances only: no table to outgrow
+    model_type: str = "nununex"
+    tie_word_embeddings: bool = False
+    raw: dict = field(default_factory=dict, repr=False)
+
+    MIXERS = {"general_delta": GeneralDeltaConfig, "parallel": ParallelMixerConfig, "mamba1": SelectiveScanConfig}
+
+    @classmethod
+    def from_json(cls, c: dict) -> "NununexConfig":
+        layers = []
+        for i, entry in enumerate(c["layers"]):
+            kind = entry["type"]
+            if kind not in cls.MIXERS:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            layers.append(NununexLayerConfig(kind, cls.MIXERS[kind].from_json(entry["mixer"]),
+                                             ScaledMoEConfig.from_json(entry.get("mlp"))))
+        bg = (c.get("embedding") or {}).get("bigram")
+        if not bg:
+            raise ValueError("embedding.bigram is missing")
+        taps = int((c.get("canon") or {}).get("taps", 1))
+        if taps < 1:
+            raise ValueError(f"canon.taps {taps}")
+        return cls(vocab_size=int(c["vocab"]), hidden_size=int(c["width"]),
+                   rms_norm_eps=float((c.get("norm") or {}).get("eps", 1e-6)), canon_taps=taps,
+                   logit_softcap=float(c.get("logit_softcap", 0.0) or 0.0), buckets=int(bg["buckets"]),
+                   mul_prev=int(bg["mul_prev"]), mul_cur=int(bg["mul_cur"]), layers=layers, raw=c)
+
+    # ---- the names the cache manager and the runner read from an HF config --------------------------
+    def _attn(self):
+        return [l.mixer.left for l in self.layers if l.mixer_type == "parallel"]
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.layers)
+
+    @property
+    def num_key_value_heads(self) -> int:
+        return max([a.kv_heads for a in self._attn()] or [1])
+
+    @property
+    def num_attention_heads(self) -> int:
+        return max([a.heads for a in self._attn()] or [1])
+
+    @property
+    def head_dim(self) -> int:
+        return max([a.dim for a in self._attn()] or [1])
+
+
+ARCHITECTURES = {"Movolorn": MovolornConfig, "Batasun": BatasunConfig, "Fafelix": FafelixConfig,
+                 "Nununex": NununexConfig}
 
 
 def load_model_config(path: str):

@@ -340,7 +340,9 @@ class ModelRunner:
                 set_context(is_prefill=False, batch_mapping=slots, positions_i32=pos, token_slot=slots,
                             max_seqlen_q=1, max_seqlen_k=self.config.max_model_len)
                 hidden = self.model(ids, pos.long())
-                out = self.model.lm_head(hidden)
+                # every row's logits: the model's own head function when it has one (a cap on the logits, say)
+                head = getattr(self.model, "compute_all_logits", self.model.lm_head)
+                out = head(hidden)
                 reset_context()
                 return out, self.sampler(out, pk[3 * bs:].view(torch.float32))
 

@@ -135,6 +135,22 @@ def pair_rotation_frequencies(dims: int, base: float, scaling: Optional[tuple] =
     return torch.tensor(out, dtype=torch.float64)
 
 
+def distance_buckets(rows: int, far: int, length: int) -> list:
+    """Row of a learned distance-bias table of `rows` rows for the distances 0 .. length - 1: distances below
+    rows // 2 have a row each, larger ones share logarithmic buckets that reach the last row at distance `far`:
+    bucket(n) = min(rows - 1, half + floor(ln(n / half) / ln(far / half) * (rows - half))), half = rows // 2."""
+    import math
+
+    half = rows // 2
+    out = []
+    for n in range(length):
+        if n < half or half == 0:
+            out.append(min(n, rows - 1))
+        else:
+            out.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    return out
+
+
 class BiasedChunkAttention(nn.Module):
     """Attention over the paged cache for models without rotation (csrc/bias_attn.cu):
 
@@ -146,7 +162,10 @@ class BiasedChunkAttention(nn.Module):
     `sink` False = plain softmax; `learned_sink` gives every head its own sink score (a parameter, not scaled; without
     it the score is 0).  `rotation` (inv_freq [rot_dims / 2] float64, see `pair_rotation_frequencies`) turns
     neighbouring pairs (2 i, 2 i + 1) of the first rot_dims numbers of every q and k head by position * inv_freq[i]
-    BEFORE the norm; `norm` False leaves q and k unnormed.  forward() takes the packed projection rows
+    BEFORE the norm; `norm` False leaves q and k unnormed.  `window` > 0: a query sees only the keys at distances
+    0 .. window - 1.  `bucket_bias` = (rows, far): a learned table `rel` [rows, H] adds rel[bucket(i - j), h] to the
+    score (unscaled; buckets as in `distance_buckets`); the kernels read it spread out per distance (`dist_bias`,
+    rebuilt by `refresh_distance_bias()` whenever `rel` changes).  forward() takes the packed projection rows
     [T, H*D + G*D + G*Dv] (row stride free): one launch rotates / norms q / k
     and writes k / v to the cache at the tokens' positions, one launch attends — the portion kernel when any
     sequence of the step brings more than one token, the decode kernel otherwise.  The step's geometry comes from the
@@ -156,9 +175,17 @@ class BiasedChunkAttention(nn.Module):
     def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float, *,
                  slopes: Optional[torch.Tensor] = None, chunk: int = 0, sink: bool = False, qk_norm: bool = False,
                  eps: float = 1e-6, values_in_keys: bool = False, learned_sink: bool = False,
-                 rotation: Optional[torch.Tensor] = None, norm: bool = True):
+                 rotation: Optional[torch.Tensor] = None, norm: bool = True, window: int = 0,
+                 bucket_bias: Optional[tuple] = None):
         super().__init__()
         self.norm = bool(norm)
+        self.window = int(window)
+        self.bias_far = 0
+        self.rel = None
+        if bucket_bias is not None:
+            rows, self.bias_far = int(bucket_bias[0]), int(bucket_bias[1])
+            self.rel = nn.Parameter(torch.zeros(rows, num_heads, dtype=torch.float32))
+        self.register_buffer("dist_bias", None, persistent=False)
         self.sink_logits = nn.Parameter(torch.zeros(num_heads, dtype=torch.float32)) if learned_sink else None
         if rotation is not None:
             assert rotation.dtype == torch.float64 and 2 * rotation.numel() <= head_dim
@@ -177,6 +204,19 @@ class BiasedChunkAttention(nn.Module):
         self.bh_seq_lens: Optional[torch.Tensor] = None
         self.page_size: Optional[int] = None
 
+    @torch.no_grad()
+    def refresh_distance_bias(self, rel: Optional[torch.Tensor] = None) -> None:
+        """`rel` (given: the new table, any number of rows) spread out per distance: dist_bias[n, h] =
+        rel[bucket(n), h] for n up to where the buckets (or the window) end; larger distances read the last row."""
+        if rel is not None:
+            self.rel = nn.Parameter(rel.detach().to(device=self.rel.device, dtype=torch.float32).contiguous())
+        rows = self.rel.shape[0]
+        length = self.bias_far + 1
+        if self.window > 0:
+            length = min(length, self.window)
+        idx = torch.tensor(distance_buckets(rows, self.bias_far, max(length, 1)), dtype=torch.long, device=self.rel.device)
+        self.dist_bias = self.rel.detach().index_select(0, idx).contiguous()
+
     @property
     def qkv_width(self) -> int:
         return (self.num_heads + self.num_kv_heads) * self.head_dim + self.num_kv_heads * self.v_head_dim
@@ -189,6 +229,8 @@ class BiasedChunkAttention(nn.Module):
         again to the merge pass when the bound `max_keys` is well above the keys really there (graph replays).
         `max_keys` bounds the keys a query can see (the chunk bounds it further)."""
         keys = min(max_keys, self.chunk) if self.chunk else max_keys
+        if self.window:
+            keys = min(keys, self.window)
         ctas = max(batch * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 4), 1)
         one_wave = min(296 // ctas, keys // 128)
         several = min(2048 // ctas, keys // 1024)
@@ -236,20 +278,24 @@ class BiasedChunkAttention(nn.Module):
             # the values are dropped on return.
             Dv = D
         out = torch.empty((T, H, Dv), dtype=q.dtype, device=dev)
+        if self.rel is not None and self.dist_bias is None:
+            self.refresh_distance_bias()
+        db = self.dist_bias
+        dist = (self.window, N.ptr(db), 0 if db is None else db.shape[0])
         if ctx.is_prefill:
             B = ctx.batch_mapping.numel()
-            N.check(lib.cvllm_bias_attn_varlen(
+            N.check(lib.cvllm_bias_attn_varlen_dist(
                 N.ptr(q), N.ptr(self.k_cache), N.ptr(v_cache), *table, N.ptr(ctx.cu_seqlens_q),
-                N.ptr(ctx.seq_start), N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink),
+                N.ptr(ctx.seq_start), N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, *dist, int(self.sink),
                 N.ptr(self.sink_logits), self.scale, N.ptr(out), B, int(ctx.max_seqlen_q), H, G, D, Dv, T, self.k_cache.shape[0], pt.shape[-1],
                 v_stride, code, N.stream(dev)), "cvllm_bias_attn_varlen")
         else:
             assert ctx.batch_mapping.numel() == T
             splits = self.decode_splits(T, int(ctx.max_seqlen_k))
             ws = N.workspace(dev, 4 * T * H * splits * (2 + Dv), "bias_attn_decode") if splits > 1 else None
-            N.check(lib.cvllm_bias_attn_decode(
+            N.check(lib.cvllm_bias_attn_decode_dist(
                 N.ptr(q), N.ptr(self.k_cache), N.ptr(v_cache), *table, N.ptr(ctx.positions_i32),
-                N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink), N.ptr(self.sink_logits),
+                N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, *dist, int(self.sink), N.ptr(self.sink_logits),
                 self.scale, N.ptr(out), T, H, G, D, Dv, RESERVED_BATCH, splits, N.ptr(ws), ws.numel() if ws is not None else 0, v_stride, code,
                 N.stream(dev)), "cvllm_bias_attn_decode")
         if keep != Dv:

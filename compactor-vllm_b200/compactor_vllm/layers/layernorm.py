@@ -133,6 +133,50 @@ def residual_norm(resid: torch.Tensor, *, add: tuple = (), add_f32: torch.Tensor
     return out
 
 
+def gated_residual_norm(resid: torch.Tensor, *, branch: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                        weight: torch.Tensor | None = None, eps: float = 1e-6, out_dtype: torch.dtype | None = None):
+    """One launch of `cvllm_gated_residual_norm` on a 32-bit residual stream `resid` [T, width], updated IN PLACE:
+
+        branch given:  resid += sigmoid(gate) * branch     (gate logits and branch [T, width], bfloat16 or float32)
+        weight given:  returns resid / sqrt(mean(resid^2) + eps) * weight in `out_dtype`
+
+    i.e. the gated residual sum of one sublayer fused with the RMS norm in front of the next."""
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.stride(1) == 1
+    rows, width = resid.shape
+    y_code = g_code = o_code = N.CVLLM_F32
+    y_stride = g_stride = o_stride = 0
+    if branch is not None:
+        assert gate is not None and branch.shape == resid.shape == gate.shape
+        assert branch.stride(1) == 1 and gate.stride(1) == 1
+        y_code, y_stride = N.block_dtype_code(branch.dtype), branch.stride(0)
+        g_code, g_stride = N.block_dtype_code(gate.dtype), gate.stride(0)
+    out = None
+    if weight is not None:
+        assert weight.dtype == torch.float32
+        out = torch.empty((rows, width), dtype=out_dtype or torch.float32, device=resid.device)
+        o_code, o_stride = N.block_dtype_code(out.dtype), out.stride(0)
+    rc = N.lib().cvllm_gated_residual_norm(
+        N.ptr(branch), y_stride, y_code, N.ptr(gate) if branch is not None else None, g_stride, g_code, N.ptr(resid),
+        resid.stride(0), N.ptr(weight), N.ptr(out), o_stride, o_code, rows, width, float(eps), N.stream(resid.device))
+    N.check(rc, "cvllm_gated_residual_norm")
+    return out
+
+
+def dual_norm_blend(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, eps: float,
+                    scale: float = 0.5) -> torch.Tensor:
+    """scale * (rms_norm(a) * wa + rms_norm(b) * wb) per row (`cvllm_dual_norm_blend`): two branch outputs, each
+    RMS-normed with a weight of its own, blended; fp32 inside, the result in the branches' type."""
+    assert a.shape == b.shape and a.dtype == b.dtype and a.stride(1) == 1 and b.stride(1) == 1
+    assert wa.dtype == torch.float32 and wb.dtype == torch.float32
+    rows, width = a.shape
+    out = torch.empty((rows, width), dtype=a.dtype, device=a.device)
+    rc = N.lib().cvllm_dual_norm_blend(N.ptr(a), a.stride(0), N.ptr(wa), N.ptr(b), b.stride(0), N.ptr(wb), N.ptr(out),
+                                       out.stride(0), rows, width, float(eps), float(scale),
+                                       N.block_dtype_code(a.dtype), N.stream(a.device))
+    N.check(rc, "cvllm_dual_norm_blend")
+    return out
+
+
 class LayerNormWeight(nn.Module):
     """Gain and bias of a layer norm kept in fp32 whatever the model dtype (the norm runs inside `residual_norm`)."""
 

@@ -15,7 +15,8 @@ from compactor_vllm import _native as N
 from compactor_vllm.utils.context import get_context
 
 ACT_SILU, ACT_GELU_TANH, ACT_CLAMPED_GLU = 0, 1, 2
-ROUTE_SOFTMAX_ALL, ROUTE_TOP_LOGITS = 0, 1
+ROUTE_SOFTMAX_ALL, ROUTE_TOP_LOGITS, ROUTE_SIGMOID = 0, 1, 2
+ACT_RELU_SQUARED = 0      # kinds of `unary_act`
 
 
 def gated_act(x: torch.Tensor, kind: int, rows: int | None = None, limit: float = 0.0) -> torch.Tensor:
@@ -38,6 +39,7 @@ def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, group
     ROUTE_SOFTMAX_ALL: s = softmax(logits); the choice is made on s + correction among the experts of the `keep` best
     of `groups` neighbour groups (a group's rank is its largest s + correction); the weights are the chosen experts'
     plain s.  ROUTE_TOP_LOGITS: the `top` largest logits are chosen, the weights are the softmax over those alone.
+    ROUTE_SIGMOID: the `top` largest sigmoid(logit) are chosen, each with its own sigmoid as weight (not renormalized).
     `experts`: only the first so many columns are router outputs (the rows may carry more, e.g. a gate logit)."""
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     T, E = logits.shape
@@ -48,6 +50,29 @@ def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, group
                                  int(keep), int(mode), N.ptr(idx), N.ptr(wts), N.stream(logits.device))
     N.check(rc, "cvllm_moe_route")
     return idx, wts
+
+
+def unary_act(x: torch.Tensor, kind: int = ACT_RELU_SQUARED) -> torch.Tensor:
+    """x [T, F] (row stride free) -> act(x) [T, F] (fp32 inside).  ACT_RELU_SQUARED: relu(x) ** 2."""
+    T, F_ = x.shape
+    assert x.stride(1) == 1
+    out = torch.empty((T, F_), dtype=x.dtype, device=x.device)
+    N.check(N.lib().cvllm_unary_act(N.ptr(x), x.stride(0), N.ptr(out), out.stride(0), T, F_, int(kind),
+                                    N.block_dtype_code(x.dtype), N.stream(x.device)), "cvllm_unary_act")
+    return out
+
+
+class PlainMLP(nn.Module):
+    """down(act(up x + b) ) + b: an ungated feed-forward with biases; act = relu squared."""
+
+    def __init__(self, width: int, ff: int, act: int = ACT_RELU_SQUARED):
+        super().__init__()
+        self.act = act
+        self.up_proj = nn.Linear(width, ff, bias=True)
+        self.down_proj = nn.Linear(ff, width, bias=True)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(unary_act(self.up_proj(x), self.act))
 
 
 class GatedMLP(nn.Module):
@@ -68,7 +93,9 @@ class RoutedExperts(nn.Module):
     group-limited choice, a correction that shifts the choice but not the weights, and an optional shared expert.
     Options: `route_mode` ROUTE_TOP_LOGITS (choice on the logits, softmax over the chosen), `router_bias` (a bias on
     the logits), `limit` / `shared_limit` (clamps of ACT_CLAMPED_GLU), `shared_gate` (the shared expert's output is
-    multiplied by the sigmoid of one more router row, so `router` has a row more than there are experts).
+    multiplied by the sigmoid of one more router row, so `router` has a row more than there are experts),
+    `route_mode` ROUTE_SIGMOID (see `route`), `scale_inputs` (the routing weight multiplies the expert's INPUT, rounded
+    to the activations' type, instead of its output: the outputs are summed unweighted).
 
     The router runs in fp32.  Portions: (token, choice) pairs are sorted by expert; in bfloat16 (sizes multiples of 8)
     the two projections are library grouped GEMMs over the segments (`torch._grouped_mm`, segment ends on the device);
@@ -85,8 +112,10 @@ class RoutedExperts(nn.Module):
     def __init__(self, width: int, ff: int, experts: int, identity: int, top: int, groups: int, keep: int,
                  shared_ff: int, act: int = ACT_SILU, dtype: torch.dtype | None = None, *,
                  route_mode: int = ROUTE_SOFTMAX_ALL, router_bias: bool = False, limit: float = 0.0,
-                 shared_limit: float = 0.0, shared_gate: bool = False):
+                 shared_limit: float = 0.0, shared_gate: bool = False, scale_inputs: bool = False):
         super().__init__()
+        self.scale_inputs = bool(scale_inputs)
+        assert not (scale_inputs and identity), "identity experts have no input to scale"
         self.width, self.ff, self.n_real, self.n_identity = width, ff, experts, identity
         self.top, self.groups, self.keep, self.act = top, groups, keep, act
         self.route_mode, self.limit = int(route_mode), float(limit)
@@ -109,15 +138,24 @@ class RoutedExperts(nn.Module):
         gate = (N.ptr(logits) + 4 * self.total, logits.stride(0)) if self.shared_gate else (None, 0)
         out = torch.empty((T, W), dtype=torch.float32, device=x.device)
         lib, code, st = N.lib(), N.block_dtype_code(x.dtype), N.stream(x.device)
+        cw = None if self.scale_inputs else N.ptr(wts)     # weights of the combine (None: all 1)
+
+        def scaled(perm):     # rows of the pairs (in `perm`'s order), each times its routing weight
+            rows = torch.empty((T * self.top, W), dtype=x.dtype, device=x.device)
+            N.check(lib.cvllm_scaled_rows(N.ptr(x), x.stride(0), N.ptr(perm), N.ptr(wts), self.top, N.ptr(rows),
+                                          T * self.top, W, code, st), "cvllm_scaled_rows")
+            return rows
+
         if not get_context().is_prefill or T <= self.SMALL_STEP:
             pairs = T * self.top
             a = torch.empty((pairs, self.ff), dtype=x.dtype, device=x.device)
             ys = torch.empty((pairs, W), dtype=x.dtype, device=x.device)
-            N.check(lib.cvllm_expert_gemv(N.ptr(x), self.top, N.ptr(self.gate_up), N.ptr(idx), self.n_real, N.ptr(a),
+            src, div = (scaled(None), 1) if self.scale_inputs else (x, self.top)
+            N.check(lib.cvllm_expert_gemv(N.ptr(src), div, N.ptr(self.gate_up), N.ptr(idx), self.n_real, N.ptr(a),
                                           pairs, self.ff, W, self.act, self.limit, code, st), "cvllm_expert_gemv")
             N.check(lib.cvllm_expert_gemv(N.ptr(a), 1, N.ptr(self.down), N.ptr(idx), self.n_real, N.ptr(ys),
                                           pairs, W, self.ff, -1, 0.0, code, st), "cvllm_expert_gemv")
-            N.check(lib.cvllm_moe_combine(N.ptr(ys), None, N.ptr(wts), self.top, N.ptr(idx), self.n_real, N.ptr(x),
+            N.check(lib.cvllm_moe_combine(N.ptr(ys), None, cw, self.top, N.ptr(idx), self.n_real, N.ptr(x),
                                           N.ptr(shared), *gate, N.ptr(out), T, W, code, st), "cvllm_moe_combine")
             return out
         # pairs sorted by expert (identity experts' pairs come last and are never multiplied); every buffer has
@@ -126,7 +164,7 @@ class RoutedExperts(nn.Module):
         order = torch.argsort(flat, stable=True)
         pos = torch.empty_like(order, dtype=torch.int32)
         pos[order] = torch.arange(order.numel(), dtype=torch.int32, device=x.device)
-        xs = x.index_select(0, order // self.top)
+        xs = scaled(order) if self.scale_inputs else x.index_select(0, order // self.top)
         counts = torch.zeros(self.n_real + self.n_identity, dtype=torch.int32, device=x.device)
         counts.index_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))
         ys = None
@@ -155,6 +193,6 @@ class RoutedExperts(nn.Module):
                 if c:
                     torch.mm(a[off:off + c], self.down[e].t(), out=ys[off:off + c])
                     off += c
-        N.check(lib.cvllm_moe_combine(N.ptr(ys), N.ptr(pos), N.ptr(wts), self.top, N.ptr(idx), self.n_real, N.ptr(x),
+        N.check(lib.cvllm_moe_combine(N.ptr(ys), N.ptr(pos), cw, self.top, N.ptr(idx), self.n_real, N.ptr(x),
                                       N.ptr(shared), *gate, N.ptr(out), T, W, code, st), "cvllm_moe_combine")
         return out

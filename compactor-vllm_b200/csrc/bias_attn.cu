@@ -46,6 +46,27 @@ inline PagedKV make_paged(const void* k, const void* v, const int32_t* table, in
   return PagedKV{k, v, table, stride_slot, stride_head, page_size, shift, v_stride};
 }
 
+// A sliding window and a learned bias per distance, beside the linear bias and the chunk mask (all may be combined):
+// a query at position i sees the keys at distances 0 .. window - 1 (window 0: no limit), and the score of the key at
+// distance n gets table[min(n, rows - 1), h] (fp32 [rows, H]; NULL: none).  The table is made by the caller, so any
+// rule from distance to bias (buckets of a smaller learned table, for one) is served.
+struct DistBias {
+  const float* table;
+  int rows;
+  int window;
+};
+
+__device__ __forceinline__ float dist_bias_at(const DistBias& db, int n, int H, int h) {
+  return db.table ? db.table[(int64_t)min(n, db.rows - 1) * H + h] : 0.f;
+}
+
+// first position a query at position pi sees
+__device__ __forceinline__ int first_key(int pi, int chunk, const DistBias& db) {
+  int lo = chunk > 0 ? (pi / chunk) * chunk : 0;
+  if (db.window > 0) lo = max(lo, pi - db.window + 1);
+  return lo;
+}
+
 __device__ __forceinline__ int64_t cache_row(const PagedKV& c, int slot, int g, int pos) {
   const int lp = c.page_shift >= 0 ? pos >> c.page_shift : pos / c.page_size;
   const int page = c.table[slot * c.table_stride_slot + g * c.table_stride_head + lp];
@@ -146,7 +167,7 @@ constexpr int BM = 64;
 template <typename T, int BN, int DVC>
 __global__ void __launch_bounds__(256) bias_attn_varlen_kernel(
     const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ seq_start,
-    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale,
     T* __restrict__ out, int H, int G, int D, int Dv) {
   constexpr int NJ = BN / 16;
   const int b = blockIdx.y, h = blockIdx.z;
@@ -158,7 +179,7 @@ __global__ void __launch_bounds__(256) bias_attn_varlen_kernel(
   const int start = seq_start[b];
   const int rows = min(BM, n_new - tile0);
   const int p_first = start + tile0, p_last = p_first + rows - 1;
-  const int lo = chunk > 0 ? (p_first / chunk) * chunk : 0;
+  const int lo = first_key(p_first, chunk, db);
   const float slope = slopes ? slopes[h] : 0.f;
 
   extern __shared__ float smem[];
@@ -220,13 +241,13 @@ __global__ void __launch_bounds__(256) bias_attn_varlen_kernel(
     for (int i = 0; i < 4; ++i) {
       const int r = ty * 4 + i;
       const int pi = p_first + r;
-      const int lo_i = chunk > 0 ? (pi / chunk) * chunk : 0;
+      const int lo_i = first_key(pi, chunk, db);
       float mx = -INFINITY;
 #pragma unroll
       for (int j = 0; j < NJ; ++j) {
         const int pj = k0 + tx + 16 * j;
         const bool ok = r < rows && pj <= pi && pj >= lo_i;
-        s[i][j] = ok ? s[i][j] * scale - slope * (float)(pi - pj) : -INFINITY;
+        s[i][j] = ok ? s[i][j] * scale - slope * (float)(pi - pj) + dist_bias_at(db, pi - pj, H, h) : -INFINITY;
         mx = fmaxf(mx, s[i][j]);
       }
 #pragma unroll
@@ -312,7 +333,7 @@ template <int DMAX>
 __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
     const __nv_bfloat16* __restrict__ q, PagedKV c, const int32_t* __restrict__ cu_q,
     const int32_t* __restrict__ seq_start, const int32_t* __restrict__ batch_mapping,
-    const float* __restrict__ slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, __nv_bfloat16* __restrict__ out, int H, int G,
+    const float* __restrict__ slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale, __nv_bfloat16* __restrict__ out, int H, int G,
     int D, int Dv) {
   constexpr int BN = 64, LD = DMAX + 8, KS = DMAX / 16, NV = DMAX / 8;
   constexpr float kL2e = 1.4426950408889634f;   // scores in log2 units: one ex2.approx per exponential
@@ -329,7 +350,7 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
   const int g = h / (H / G);
   const int rows = min(BM, n_new - tile0);
   const int p_first = seq_start[b] + tile0, p_last = p_first + rows - 1;
-  const int lo = chunk > 0 ? (p_first / chunk) * chunk : 0;
+  const int lo = first_key(p_first, chunk, db);
   const float slope2 = slopes ? slopes[h] * kL2e : 0.f;
   const float scale2 = scale * kL2e;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quad = lane >> 2, tq = lane & 3;
@@ -377,11 +398,11 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[nb][e] = 0.f;
   const int pi_lo = p_first + r_lo, pi_hi = p_first + r_hi;
-  const int lo_lo = chunk > 0 ? (pi_lo / chunk) * chunk : 0, lo_hi = chunk > 0 ? (pi_hi / chunk) * chunk : 0;
+  const int lo_lo = first_key(pi_lo, chunk, db), lo_hi = first_key(pi_hi, chunk, db);
   // a tile needs no masks for this warp when all its keys are at or before the warp's first row and inside the
   // chunk of the warp's last row (rows beyond `rows` are never written, their values do not matter)
   const int warp_first = p_first + warp * 16;
-  const int warp_lo = chunk > 0 ? ((warp_first + 15) / chunk) * chunk : 0;
+  const int warp_lo = first_key(warp_first + 15, chunk, db);
 
   int stage = 0;
   for (int k0 = lo; k0 <= p_last; k0 += BN, stage ^= 1) {
@@ -419,7 +440,8 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int pj = k0 + nb * 8 + tq * 2 + (e & 1);
-          s[nb][e] = s[nb][e] * scale2 - slope2 * (float)(((e & 2) ? pi_hi : pi_lo) - pj);
+          const int dist = ((e & 2) ? pi_hi : pi_lo) - pj;
+          s[nb][e] = s[nb][e] * scale2 - slope2 * (float)dist + dist_bias_at(db, dist, H, h) * kL2e;
           mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
         }
     } else {
@@ -431,7 +453,8 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
           const int pi = (e & 2) ? pi_hi : pi_lo;
           const int lo_i = (e & 2) ? lo_hi : lo_lo;
           const bool ok = ((e & 2) ? r_hi : r_lo) < rows && pj <= pi && pj >= lo_i;
-          s[nb][e] = ok ? s[nb][e] * scale2 - slope2 * (float)(pi - pj) : -INFINITY;
+          s[nb][e] = ok ? s[nb][e] * scale2 - slope2 * (float)(pi - pj) + dist_bias_at(db, pi - pj, H, h) * kL2e
+                        : -INFINITY;
           mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
         }
     }
@@ -504,14 +527,14 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
 
 template <int DMAX>
 int launch_varlen_mma(const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start, const int32_t* bm,
-                      const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out, int B, int max_new, int H,
+                      const float* slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale, void* out, int B, int max_new, int H,
                       int G, int D, int Dv, cudaStream_t st) {
   static std::atomic<uint64_t> mask{0};
   const int smem = 4 * 64 * (DMAX + 8) * 2;
   auto kern = bias_attn_varlen_mma_kernel<DMAX>;
   CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), smem, mask));
   dim3 grid(cdiv(max_new, BM), B, H);
-  kern<<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), c, cu_q, seq_start, bm, slopes, chunk, sink, sink_logits,
+  kern<<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), c, cu_q, seq_start, bm, slopes, chunk, db, sink, sink_logits,
                                 scale, static_cast<__nv_bfloat16*>(out), H, G, D, Dv);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
@@ -528,7 +551,7 @@ constexpr int kDecCols = 16;  // output columns per lane: Dv <= 512
 template <typename T>
 __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
     const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ positions,
-    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale,
     T* __restrict__ out, int H, int G, int D, int Dv, int reserved_slot) {
   extern __shared__ float smem[];
   float* qs = smem;                         // [D]
@@ -543,7 +566,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
   }
   const int g = h / (H / G);
   const int pi = positions[b];
-  const int lo = chunk > 0 ? (pi / chunk) * chunk : 0;
+  const int lo = first_key(pi, chunk, db);
   const float slope = slopes ? slopes[h] : 0.f;
   for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = to_f<T>(q[((int64_t)b * H + h) * D + d]);
   __syncthreads();
@@ -561,7 +584,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
       const T* kr = kc + row * D;
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_f<T>(kr[d]), dot);
-      s = dot * scale - slope * (float)(pi - pj);
+      s = dot * scale - slope * (float)(pi - pj) + dist_bias_at(db, pi - pj, H, h);
     }
     const float m_new = fmaxf(m, warp_max(s));  // lane 0 of the batch is always a live key
     const float corr = expf(m - m_new);
@@ -723,7 +746,7 @@ __global__ void __launch_bounds__(128) qknorm_store_vec_kernel(
 template <typename T, int CH>
 __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
     const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ positions,
-    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale,
     T* __restrict__ out, float* __restrict__ part, int H, int G, int D, int Dv, int splits, int reserved_slot) {
   __shared__ float qs[kDecTile][64 * CH];
   __shared__ float st[4][kDecTile][2 + 64 * CH];
@@ -747,7 +770,7 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
     return;
   }
   const int pi = positions[b];
-  const int lo = chunk > 0 ? (pi / chunk) * chunk : 0;
+  const int lo = first_key(pi, chunk, db);
   const int n = pi - lo + 1, per = (n + splits - 1) / splits;
   const int k_begin = lo + split * per, k_end = min(pi + 1, k_begin + per);
   for (int i = tid; i < kDecTile * D; i += 128) {
@@ -862,6 +885,7 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
       v += __shfl_xor_sync(gmask, v, 2);
       v += __shfl_xor_sync(gmask, v, 1);
       v -= slope[r] * dist;
+      if (db.table != nullptr && r < nr) v += dist_bias_at(db, pi - j, H, h0 + r) * kLog2e;
       // The reference point m moves only when a logit passes it by more than kDecSlack (log2 units): weights stay
       // below 2^kDecSlack, far inside fp32, and the result is the same sum.  With a distance bias the logits of
       // later keys keep rising, so an exact running maximum would rescale the accumulators at almost every key.
@@ -971,14 +995,14 @@ __global__ void __launch_bounds__(128) bias_attn_decode_merge_kernel(const float
 
 template <typename T, int CH>
 int launch_decode_split_ch(const void* q, const PagedKV& c, const int32_t* positions, const int32_t* bm,
-                           const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out, float* part, dim3 grid,
+                           const float* slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale, void* out, float* part, dim3 grid,
                            int H, int G, int D, int Dv, int splits, int reserved_slot, cudaStream_t st) {
   // the ring: stages x (K | V) x CH chunks x 16-byte pieces per chunk x 128 threads x 16 bytes
   const size_t ring = (size_t)(CH <= 2 ? 4 : 2) * 2 * CH * (8 / (16 / sizeof(T))) * 128 * 16;
   static std::atomic<uint64_t> mask{0};
   auto kern = bias_attn_decode_split_kernel<T, CH>;
   CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)ring, mask));
-  kern<<<grid, 128, ring, st>>>(static_cast<const T*>(q), c, positions, bm, slopes, chunk, sink, sink_logits, scale,
+  kern<<<grid, 128, ring, st>>>(static_cast<const T*>(q), c, positions, bm, slopes, chunk, db, sink, sink_logits, scale,
                                 static_cast<T*>(out), part, H, G, D, Dv, splits, reserved_slot);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
@@ -986,14 +1010,14 @@ int launch_decode_split_ch(const void* q, const PagedKV& c, const int32_t* posit
 
 template <typename T>
 int launch_decode_split(const void* q, const PagedKV& c, const int32_t* positions, const int32_t* bm,
-                        const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out, float* part, int B, int H,
+                        const float* slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale, void* out, float* part, int B, int H,
                         int G, int D, int Dv, int splits, int reserved_slot, cudaStream_t st) {
   const int R = H / G, tiles = cdiv(R, kDecTile);
   dim3 grid(splits, G * tiles, B);
   const int ch = cdiv(D > Dv ? D : Dv, 64);
   int rc;
 #define CVLLM_GO(CH) \
-  rc = launch_decode_split_ch<T, CH>(q, c, positions, bm, slopes, chunk, sink, sink_logits, scale, out, part, grid, H, G, D, Dv, \
+  rc = launch_decode_split_ch<T, CH>(q, c, positions, bm, slopes, chunk, db, sink, sink_logits, scale, out, part, grid, H, G, D, Dv, \
                                      splits, reserved_slot, st)
   if (ch == 1) CVLLM_GO(1);
   else if (ch == 2) CVLLM_GO(2);
@@ -1014,14 +1038,14 @@ size_t varlen_smem(int BN, int D, int Dv) {
 
 template <typename T, int BN, int DVC>
 int launch_varlen(const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start,
-                  const int32_t* batch_mapping, const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out,
+                  const int32_t* batch_mapping, const float* slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale, void* out,
                   int B, int max_new, int H, int G, int D, int Dv, cudaStream_t st) {
   static std::atomic<uint64_t> mask{0};
   const size_t smem = varlen_smem(BN, D, Dv);
   auto kern = bias_attn_varlen_kernel<T, BN, DVC>;
   CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), 226 * 1024, mask));
   dim3 grid(cdiv(max_new, BM), B, H);
-  kern<<<grid, 256, smem, st>>>(static_cast<const T*>(q), c, cu_q, seq_start, batch_mapping, slopes, chunk, sink, sink_logits,
+  kern<<<grid, 256, smem, st>>>(static_cast<const T*>(q), c, cu_q, seq_start, batch_mapping, slopes, chunk, db, sink, sink_logits,
                                 scale, static_cast<T*>(out), H, G, D, Dv);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
@@ -1029,10 +1053,10 @@ int launch_varlen(const void* q, const PagedKV& c, const int32_t* cu_q, const in
 
 template <typename T, int BN>
 int dispatch_dvc(int dvc, const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start,
-                 const int32_t* bm, const float* slopes, int chunk, float sink, const float* __restrict__ sink_logits, float scale, void* out, int B,
+                 const int32_t* bm, const float* slopes, int chunk, DistBias db, float sink, const float* __restrict__ sink_logits, float scale, void* out, int B,
                  int max_new, int H, int G, int D, int Dv, cudaStream_t st) {
 #define CVLLM_GO(N) \
-  return launch_varlen<T, BN, N>(q, c, cu_q, seq_start, bm, slopes, chunk, sink, sink_logits, scale, out, B, max_new, H, G, D, Dv, st)
+  return launch_varlen<T, BN, N>(q, c, cu_q, seq_start, bm, slopes, chunk, db, sink, sink_logits, scale, out, B, max_new, H, G, D, Dv, st)
   if (dvc <= 4) CVLLM_GO(4);
   if (dvc <= 6) CVLLM_GO(6);
   if (dvc <= 8) CVLLM_GO(8);
@@ -1135,7 +1159,24 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
                                       const float* sink_logits, float scale, void* out, int B, int max_new, int H, int G, int D, int Dv,
                                       int total_tokens, int64_t cache_rows, int pages_per_head, int64_t v_stride,
                                       int dtype, cvllm_stream_t stream) {
+  return cvllm_bias_attn_varlen_dist(q, k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size,
+                                     cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, 0, nullptr, 0, sink,
+                                     sink_logits, scale, out, B, max_new, H, G, D, Dv, total_tokens, cache_rows,
+                                     pages_per_head, v_stride, dtype, stream);
+}
+
+extern "C" int cvllm_bias_attn_varlen_dist(const void* q, const void* k_cache, const void* v_cache,
+                                           const int32_t* page_table, int64_t table_stride_slot,
+                                           int64_t table_stride_head, int page_size, const int32_t* cu_seqlens_q,
+                                           const int32_t* seq_start, const int32_t* batch_mapping, const float* slopes,
+                                           int chunk, int window, const float* dist_bias, int dist_rows, int sink,
+                                           const float* sink_logits, float scale, void* out, int B, int max_new, int H,
+                                           int G, int D, int Dv, int total_tokens, int64_t cache_rows,
+                                           int pages_per_head, int64_t v_stride, int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0);
+  CVLLM_CHECK_ARG(window >= 0 && (dist_bias == nullptr || dist_rows > 0));
+  const DistBias db{dist_bias, dist_rows, window};
+  const bool plain_bias = window == 0 && dist_bias == nullptr;   // what the tcgen05 pipeline serves
   if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && cu_seqlens_q && seq_start && batch_mapping && out &&
                   check_dtype(dtype) && page_size > 0);
@@ -1152,11 +1193,11 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
   while (bn > 32 && varlen_smem(bn, D, Dv) > cap) bn >>= 1;
   CVLLM_CHECK_SUPPORTED(varlen_smem(bn, D, Dv) <= cap);
 #define CVLLM_GO(T, BN) \
-  return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, sink_logits, scale, out, B, \
+  return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, db, fs, sink_logits, scale, out, B, \
                              max_new, H, G, D, Dv, st)
   const int path = test_options().bias_attn_fma.load();   // 0 product, 1 fp32 FMA kernel, 2 no tcgen05 kernel
   if (dtype == CVLLM_BF16 && D == 128 && Dv == 128 && v_stride == Dv && page_size % 128 == 0 && (H / G) % 2 == 0 &&
-      path == 0 &&
+      path == 0 && plain_bias &&
       table_stride_head == pages_per_head && table_stride_slot == (int64_t)G * pages_per_head && cache_rows > 0)
     return cvllm_launch_prefill_bias(q, k_cache, v_cache, cache_rows, out, seq_start, slopes, page_table,
                                      batch_mapping, cu_seqlens_q, B, total_tokens, H, G, page_size, pages_per_head,
@@ -1164,9 +1205,9 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
   if (dtype == CVLLM_BF16 && D % 16 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && path != 1 &&
       v_stride % vec == 0 && aligned16(k_cache) && aligned16(v_cache)) {
     if (D <= 64 && Dv <= 64)
-      return launch_varlen_mma<64>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, sink_logits, scale, out, B,
+      return launch_varlen_mma<64>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, db, fs, sink_logits, scale, out, B,
                                    max_new, H, G, D, Dv, st);
-    return launch_varlen_mma<128>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, sink_logits, scale, out, B,
+    return launch_varlen_mma<128>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, db, fs, sink_logits, scale, out, B,
                                   max_new, H, G, D, Dv, st);
   }
   if (dtype == CVLLM_BF16) {
@@ -1184,7 +1225,23 @@ extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const 
                                       const float* slopes, int chunk, int sink, const float* sink_logits, float scale,
                                       void* out, int B, int H, int G, int D, int Dv, int reserved_slot, int splits, float* workspace,
                                       size_t workspace_bytes, int64_t v_stride, int dtype, cvllm_stream_t stream) {
+  return cvllm_bias_attn_decode_dist(q, k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size,
+                                     positions, batch_mapping, slopes, chunk, 0, nullptr, 0, sink, sink_logits, scale,
+                                     out, B, H, G, D, Dv, reserved_slot, splits, workspace, workspace_bytes, v_stride,
+                                     dtype, stream);
+}
+
+extern "C" int cvllm_bias_attn_decode_dist(const void* q, const void* k_cache, const void* v_cache,
+                                           const int32_t* page_table, int64_t table_stride_slot,
+                                           int64_t table_stride_head, int page_size, const int32_t* positions,
+                                           const int32_t* batch_mapping, const float* slopes, int chunk, int window,
+                                           const float* dist_bias, int dist_rows, int sink, const float* sink_logits,
+                                           float scale, void* out, int B, int H, int G, int D, int Dv,
+                                           int reserved_slot, int splits, float* workspace, size_t workspace_bytes,
+                                           int64_t v_stride, int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(B >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0 && splits >= 1);
+  CVLLM_CHECK_ARG(window >= 0 && (dist_bias == nullptr || dist_rows > 0));
+  const DistBias db{dist_bias, dist_rows, window};
   if (B == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && positions && batch_mapping && out && check_dtype(dtype) &&
                   page_size > 0);
@@ -1204,9 +1261,9 @@ extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const 
     }
     const float fs = sink ? 1.f : 0.f;
     if (dtype == CVLLM_BF16)
-      return launch_decode_split<__nv_bfloat16>(q, c, positions, batch_mapping, slopes, chunk, fs, sink_logits, scale, out,
+      return launch_decode_split<__nv_bfloat16>(q, c, positions, batch_mapping, slopes, chunk, db, fs, sink_logits, scale, out,
                                                 workspace, B, H, G, D, Dv, splits, reserved_slot, st);
-    return launch_decode_split<float>(q, c, positions, batch_mapping, slopes, chunk, fs, sink_logits, scale, out, workspace, B, H,
+    return launch_decode_split<float>(q, c, positions, batch_mapping, slopes, chunk, db, fs, sink_logits, scale, out, workspace, B, H,
                                       G, D, Dv, splits, reserved_slot, st);
   }
   const size_t smem = sizeof(float) * ((size_t)D + (size_t)kDecWarps * (2 + Dv));
@@ -1214,11 +1271,11 @@ extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const 
   dim3 grid(B, H);
   if (dtype == CVLLM_BF16)
     bias_attn_decode_kernel<__nv_bfloat16><<<grid, kDecWarps * 32, smem, st>>>(
-        static_cast<const __nv_bfloat16*>(q), c, positions, batch_mapping, slopes, chunk, sink ? 1.f : 0.f, sink_logits, scale,
+        static_cast<const __nv_bfloat16*>(q), c, positions, batch_mapping, slopes, chunk, db, sink ? 1.f : 0.f, sink_logits, scale,
         static_cast<__nv_bfloat16*>(out), H, G, D, Dv, reserved_slot);
   else
     bias_attn_decode_kernel<float><<<grid, kDecWarps * 32, smem, st>>>(
-        static_cast<const float*>(q), c, positions, batch_mapping, slopes, chunk, sink ? 1.f : 0.f, sink_logits, scale,
+        static_cast<const float*>(q), c, positions, batch_mapping, slopes, chunk, db, sink ? 1.f : 0.f, sink_logits, scale,
         static_cast<float*>(out), H, G, D, Dv, reserved_slot);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;

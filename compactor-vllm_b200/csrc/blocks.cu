@@ -265,7 +265,8 @@ constexpr int kRouteWarps = 4;
 // One warp per token.  mode 0: s = softmax(logits); choice = s + correction; experts outside the `keep` groups with
 // the largest group maximum of choice are struck; the `top` largest remaining choices are taken, each with
 // its plain s as weight.  mode 1: the `top` largest LOGITS are taken (lowest index first among equals) and the
-// weights are the softmax over the chosen logits alone.  Shared memory per warp: s[E], choice[E], group maxima[groups].
+// weights are the softmax over the chosen logits alone.  mode 2: the same choice (the largest sigmoid(logit) are the
+// largest logits), each with its own sigmoid(logit) as weight, not renormalized.  Shared memory per warp: s[E], choice[E], group maxima[groups].
 __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
     const float* __restrict__ logits, int64_t l_stride, const float* __restrict__ correction, int T, int E,
     int top, int groups, int keep, int mode, int32_t* __restrict__ idx, float* __restrict__ wts) {
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
   float* c = s + E;
   float* gm = c + E;
   const float* z = logits + (int64_t)t * l_stride;
-  if (mode == 1) {
+  if (mode == 1 || mode == 2) {
     for (int e = lane; e < E; e += 32) c[e] = z[e];
     __syncwarp();
     float zmax = 0.f, sum = 0.f;
@@ -286,7 +287,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
       const int e = warp_argmax(c, E, &b);
       __syncwarp();
       if (r == 0) zmax = b;               // the first choice is the largest logit
-      const float p = expf(b - zmax);
+      const float p = mode == 2 ? 1.0f / (1.0f + expf(-b)) : expf(b - zmax);
       sum += p;
       if (lane == 0) {
         idx[(int64_t)t * top + r] = e;
@@ -295,7 +296,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
       }
       __syncwarp();
     }
-    if (lane < top) wts[(int64_t)t * top + lane] /= sum;   // top <= 32 in this mode (checked by the host)
+    if (mode == 1 && lane < top) wts[(int64_t)t * top + lane] /= sum;   // top <= 32 in this mode (checked by the host)
     return;
   }
   float m = -INFINITY;
@@ -347,7 +348,8 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
   }
 }
 
-// out[t, :] = sum_r w[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :])  (+ s_t shared[t, :]),  fp32 sums.
+// out[t, :] = sum_r w[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :])  (+ s_t shared[t, :]),  fp32 sums;
+// w == NULL: every weight is 1 (experts whose weight went into their input).
 // pos maps a (token, choice) pair to its row of y (the pairs sorted by expert); NULL = the pair's own index.
 // s_t = sigmoid(shared_gate[t * gate_stride]) when shared_gate is given (one logit per token), else 1.
 template <typename T>
@@ -364,7 +366,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int32_t* __res
     float acc = shared ? to_f<T>(shared[i]) : 0.f;
     if (shared && shared_gate) acc *= 1.0f / (1.0f + expf(-shared_gate[t * gate_stride]));
     for (int r = 0; r < top; ++r) {
-      const float wr = w[t * top + r];
+      const float wr = w ? w[t * top + r] : 1.0f;
       if (idx[t * top + r] >= n_real)
         acc += wr * to_f<T>(h[i]);
       else
@@ -409,6 +411,100 @@ __global__ void __launch_bounds__(256) expert_gemv_kernel(const T* __restrict__ 
     a = gated<KIND>(a, b, limit);
   }
   if (lane == 0) out[(int64_t)p * N + n] = from_f<T>(a);
+}
+
+// One CTA per row of a 32-bit residual stream, for layers whose sublayer outputs pass a gate on the way in:
+//   resid += sigmoid(gate) * y      (y of type TY, gate logits of type TG, both [rows, width]; y == NULL: no sum)
+//   out = resid / sqrt(mean(resid^2) + eps) * w          (out == NULL: the sum alone)
+// i.e. the gated residual sum of one sublayer fused with the RMS norm in front of the next.
+template <typename TY, typename TG, typename TO>
+__global__ void __launch_bounds__(kThreads) gated_residual_norm_kernel(
+    const TY* __restrict__ y, int64_t y_stride, const TG* __restrict__ gate, int64_t g_stride,
+    float* __restrict__ resid, int64_t r_stride, const float* __restrict__ w, TO* __restrict__ out, int64_t o_stride,
+    int width, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[kThreads / 32];
+  const int64_t r = blockIdx.x;
+  float* res = resid + r * r_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += kThreads) {
+    float v = res[i];
+    if (y != nullptr) {
+      const float gz = to_f<TG>(gate[r * g_stride + i]);
+      v = fmaf(1.0f / (1.0f + expf(-gz)), to_f<TY>(y[r * y_stride + i]), v);
+      res[i] = v;
+    }
+    row[i] = v;
+    ss += v * v;
+  }
+  if (out == nullptr) return;
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  TO* o = out + r * o_stride;
+  for (int i = threadIdx.x; i < width; i += kThreads) o[i] = from_f<TO>(row[i] * inv * w[i]);
+}
+
+// One CTA per row: out = scale * (a / rms(a) * wa + b / rms(b) * wb), rms(v) = sqrt(mean(v^2) + eps) - two branch
+// outputs, each RMS-normed with a weight of its own, blended.  Statistics and the sum are fp32.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) dual_norm_blend_kernel(const T* __restrict__ a, int64_t a_stride,
+                                                                   const float* __restrict__ wa,
+                                                                   const T* __restrict__ b, int64_t b_stride,
+                                                                   const float* __restrict__ wb, T* __restrict__ out,
+                                                                   int64_t o_stride, int width, float eps, float scale) {
+  __shared__ float red[kThreads / 32];
+  const int64_t r = blockIdx.x;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < width; i += kThreads) {
+    const float va = to_f<T>(a[r * a_stride + i]), vb = to_f<T>(b[r * b_stride + i]);
+    sa += va * va;
+    sb += vb * vb;
+  }
+  sa = block_sum(sa, red);
+  sb = block_sum(sb, red);
+  const float ia = scale / sqrtf(sa / (float)width + eps), ib = scale / sqrtf(sb / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += kThreads)
+    out[r * o_stride + i] = from_f<T>(to_f<T>(a[r * a_stride + i]) * ia * wa[i] + to_f<T>(b[r * b_stride + i]) * ib * wb[i]);
+}
+
+// Plain activations of one tensor.  KIND 0: relu(x)^2.
+template <typename T, int KIND>
+__global__ void unary_act_kernel(const T* __restrict__ x, int64_t x_stride, T* __restrict__ out, int64_t o_stride,
+                                 int64_t rows, int F) {
+  const int64_t total = rows * (int64_t)F;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / F;
+    const int f = (int)(i - t * F);
+    const float v = fmaxf(to_f<T>(x[t * x_stride + f]), 0.f);
+    out[t * o_stride + f] = from_f<T>(v * v);
+  }
+}
+
+// out[t, c] = cap * tanh(x[t, c] / cap), fp32 out
+template <typename T>
+__global__ void softcap_kernel(const T* __restrict__ x, int64_t x_stride, float* __restrict__ out, int64_t o_stride,
+                               int64_t rows, int F, float cap) {
+  const int64_t total = rows * (int64_t)F;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / F;
+    const int f = (int)(i - t * F);
+    out[t * o_stride + f] = cap * tanhf(to_f<T>(x[t * x_stride + f]) / cap);
+  }
+}
+
+// out[p, :] = x[pair / top, :] * scale[pair], pair = perm ? perm[p] : p - the rows of (token, choice) pairs, each
+// multiplied by its routing weight on the way into its expert (rounded to the activations' type).
+template <typename T>
+__global__ void scaled_rows_kernel(const T* __restrict__ x, int64_t x_stride, const int64_t* __restrict__ perm,
+                                   const float* __restrict__ scale, int top, T* __restrict__ out, int64_t pairs,
+                                   int width) {
+  const int64_t total = pairs * (int64_t)width;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t p = i / width;
+    const int c = (int)(i - p * width);
+    const int64_t pair = perm ? perm[p] : p;
+    out[i] = from_f<T>(to_f<T>(x[(pair / top) * x_stride + c]) * scale[pair]);
+  }
 }
 
 }  // namespace
@@ -528,7 +624,7 @@ extern "C" int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64
 extern "C" int cvllm_moe_route(const float* logits, int64_t l_stride, const float* correction, int T, int E, int top,
                                int groups, int keep, int mode, int32_t* idx, float* wts, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(T >= 0 && E > 0 && top > 0 && top <= E && groups > 0 && keep > 0 && keep <= groups);
-  CVLLM_CHECK_ARG(mode == 0 || (mode == 1 && groups == 1 && correction == nullptr));
+  CVLLM_CHECK_ARG(mode == 0 || ((mode == 1 || mode == 2) && groups == 1 && correction == nullptr));
   CVLLM_CHECK_SUPPORTED(mode == 0 || top <= 32);
   if (T == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(logits && idx && wts && E % groups == 0 && keep * (E / groups) >= top);
@@ -549,7 +645,7 @@ extern "C" int cvllm_moe_combine(const void* y, const int32_t* pos, const float*
                                  float* out, int64_t rows, int width, int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(rows >= 0 && width > 0 && top > 0);
   if (rows == 0) return CVLLM_OK;
-  CVLLM_CHECK_ARG(y && w && idx && h && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
+  CVLLM_CHECK_ARG(y && idx && h && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
   auto st = static_cast<cudaStream_t>(stream);
   const int64_t total = rows * (int64_t)width;
   const int grid = (int)((total + 255) / 256 < (int64_t)sm_count() * 16 ? (total + 255) / 256 : (int64_t)sm_count() * 16);
@@ -589,6 +685,115 @@ extern "C" int cvllm_expert_gemv(const void* xs, int x_div, const void* w, const
     else CVLLM_GEMV(float, true, 2);
   }
 #undef CVLLM_GEMV
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+static int block_grid(int64_t total) {
+  const int64_t want = (total + 255) / 256, cap = (int64_t)sm_count() * 16;
+  return (int)(want < cap ? want : cap);
+}
+
+extern "C" int cvllm_gated_residual_norm(const void* y, int64_t y_stride, int y_dtype, const void* gate,
+                                         int64_t g_stride, int g_dtype, float* resid, int64_t r_stride, const float* w,
+                                         void* out, int64_t o_stride, int out_dtype, int rows, int width, float eps,
+                                         cvllm_stream_t stream) {
+  drop_stale_error();
+  CVLLM_CHECK_ARG(rows >= 0 && width > 0 && resid);
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG((y == nullptr) == (gate == nullptr));
+  CVLLM_CHECK_ARG(y == nullptr || ((y_dtype == CVLLM_BF16 || y_dtype == CVLLM_F32) &&
+                                   (g_dtype == CVLLM_BF16 || g_dtype == CVLLM_F32)));
+  CVLLM_CHECK_ARG(out == nullptr || (w != nullptr && (out_dtype == CVLLM_BF16 || out_dtype == CVLLM_F32)));
+  CVLLM_CHECK_SUPPORTED(width <= 12288);
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)width * sizeof(float);
+  const bool yb = y && y_dtype == CVLLM_BF16, gb = y && g_dtype == CVLLM_BF16, ob = out && out_dtype == CVLLM_BF16;
+#define CVLLM_GRN(TY, TG, TO)                                                                                       \
+  gated_residual_norm_kernel<TY, TG, TO><<<rows, kThreads, smem, st>>>(                                             \
+      static_cast<const TY*>(y), y_stride, static_cast<const TG*>(gate), g_stride, resid, r_stride, w,              \
+      static_cast<TO*>(out), o_stride, width, eps)
+  if (yb && gb && ob) CVLLM_GRN(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  else if (yb && gb) CVLLM_GRN(__nv_bfloat16, __nv_bfloat16, float);
+  else if (gb && ob) CVLLM_GRN(float, __nv_bfloat16, __nv_bfloat16);
+  else if (gb) CVLLM_GRN(float, __nv_bfloat16, float);
+  else if (ob) CVLLM_GRN(float, float, __nv_bfloat16);
+  else if (!yb) CVLLM_GRN(float, float, float);
+  else { set_last_error("gated_residual_norm: 16-bit branch with 32-bit gate"); return CVLLM_E_UNSUPPORTED; }
+#undef CVLLM_GRN
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_dual_norm_blend(const void* a, int64_t a_stride, const float* wa, const void* b, int64_t b_stride,
+                                     const float* wb, void* out, int64_t o_stride, int rows, int width, float eps,
+                                     float scale, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
+  CVLLM_CHECK_ARG(rows >= 0 && width > 0);
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(a && wa && b && wb && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
+  auto st = static_cast<cudaStream_t>(stream);
+  if (dtype == CVLLM_BF16)
+    dual_norm_blend_kernel<__nv_bfloat16><<<rows, kThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(a), a_stride, wa, static_cast<const __nv_bfloat16*>(b), b_stride, wb,
+        static_cast<__nv_bfloat16*>(out), o_stride, width, eps, scale);
+  else
+    dual_norm_blend_kernel<float><<<rows, kThreads, 0, st>>>(static_cast<const float*>(a), a_stride, wa,
+                                                             static_cast<const float*>(b), b_stride, wb,
+                                                             static_cast<float*>(out), o_stride, width, eps, scale);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_unary_act(const void* x, int64_t x_stride, void* out, int64_t o_stride, int64_t rows, int F,
+                               int kind, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
+  CVLLM_CHECK_ARG(rows >= 0 && F > 0 && kind == 0);
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(x && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
+  auto st = static_cast<cudaStream_t>(stream);
+  const int grid = block_grid(rows * (int64_t)F);
+  if (dtype == CVLLM_BF16)
+    unary_act_kernel<__nv_bfloat16, 0><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_stride,
+                                                             static_cast<__nv_bfloat16*>(out), o_stride, rows, F);
+  else
+    unary_act_kernel<float, 0><<<grid, 256, 0, st>>>(static_cast<const float*>(x), x_stride, static_cast<float*>(out),
+                                                     o_stride, rows, F);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_softcap(const void* x, int64_t x_stride, float* out, int64_t o_stride, int64_t rows, int F,
+                             float cap, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
+  CVLLM_CHECK_ARG(rows >= 0 && F > 0 && cap > 0.f);
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(x && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
+  auto st = static_cast<cudaStream_t>(stream);
+  const int grid = block_grid(rows * (int64_t)F);
+  if (dtype == CVLLM_BF16)
+    softcap_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_stride, out, o_stride,
+                                                        rows, F, cap);
+  else
+    softcap_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), x_stride, out, o_stride, rows, F, cap);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_scaled_rows(const void* x, int64_t x_stride, const int64_t* perm, const float* scale, int top,
+                                 void* out, int64_t pairs, int width, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
+  CVLLM_CHECK_ARG(pairs >= 0 && width > 0 && top > 0);
+  if (pairs == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(x && scale && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
+  auto st = static_cast<cudaStream_t>(stream);
+  const int grid = block_grid(pairs * (int64_t)width);
+  if (dtype == CVLLM_BF16)
+    scaled_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_stride, perm, scale,
+                                                            top, static_cast<__nv_bfloat16*>(out), pairs, width);
+  else
+    scaled_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), x_stride, perm, scale, top,
+                                                    static_cast<float*>(out), pairs, width);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
 }

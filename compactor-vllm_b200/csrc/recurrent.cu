@@ -2,13 +2,19 @@
 //
 //   gated delta rule   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //   wkv                o = (S + diag(bonus) k v^T)^T r;  S <- diag(w) S + k v^T          (w per key channel)
+//   general delta rule S <- diag(w) S - (a u)(u^T S) + k v^T  (both terms on the old S);  o = S^T r
+//                      (w, a per key channel, u the unit key)
+//   matrix memory      m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise with k alone;
+//                      o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)        (log gates i, f per head, capped)
 //
 // followed, inside the same kernel, by each head's unit norm (o / sqrt(mean(o^2) + eps)), a weight and a gate:
-// out = unit(o) * norm_w * silu(gate).  Also the token shift in front of the wkv projections.
+// out = unit(o) * norm_w * silu(gate) (or sigmoid(gate)).  Also the token shift in front of the wkv projections.
 //
 //   cvllm_token_shift_mix   out[s, t, :] = h_t + (h_(t-1) - h_t) * mu[s, :], the slot's last row carried between steps
 //   cvllm_delta_rule        unit q / k, beta, decay, the recurrence and the gated norm
 //   cvllm_wkv_scan          decays from their raw logits, the recurrence and the gated norm
+//   cvllm_general_delta     unit k, removal rates, decays, the recurrence and the gated norm
+//   cvllm_matrix_memory     capped log gates, the running maximum, the normalizer, the recurrence and the gated norm
 //
 // Geometry of a step: cu_q [B + 1] token offsets and seq_start [B] first positions of the portions, batch_mapping [B]
 // slots of the state pool; cu_q == NULL means one token per sequence at positions[b] (decode steps, CUDA-graph
@@ -180,6 +186,7 @@ struct RecurArgs {
   int H, D, Dv, reserved_slot;
   int KS, VT, CW;          // slices of the key dimension; CTAs per (head, sequence); value columns per CTA
   int tok;                 // tokens staged at a time
+  int gate_kind;           // 0: silu(gate), 1: sigmoid(gate)
 };
 
 // (row, col) of the elements e = threadIdx.x + u * blockDim.x, u = 0, 1, .., of a tile [rows, width]: one division at
@@ -249,7 +256,8 @@ __device__ __forceinline__ void gated_unit_norm_rows(const RecurArgs& a, const f
   auto emit = [&](int c, int j, float gz) {
     const int col = h * a.Dv + c0 + j;
     out[(int64_t)(tok0 + c) * a.out_stride + col] =
-        from_f<T>(so[c * a.CW + j] * sinv[c] * a.norm_w[h * a.norm_head_stride + c0 + j] * silu_f(gz));
+        from_f<T>(so[c * a.CW + j] * sinv[c] * a.norm_w[h * a.norm_head_stride + c0 + j] *
+                  (a.gate_kind ? sigmoid_f(gz) : silu_f(gz)));
   };
   TileWalk w(ncol);
 #pragma unroll
@@ -598,6 +606,261 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(const T* __restrict__ rp
   if (a.VT > 1) cooperative_groups::this_cluster().sync();   // nobody leaves while its sums may still be read
 }
 
+// General delta rule.  r, k, v, the removal-rate logits (a) and the gate are columns of proj (model type) at r_off,
+// k_off, v_off, a_off (+ h * D) and gate_off; w_raw [T, H * D] decay logits: w = exp(-rate * sigmoid(w_raw + w0)).
+// Dv = D.  With u = k / sqrt(sum k^2 + 1e-6) and au = sigmoid(a) u, per value column j from the column s before the token:
+//   d1 = u . s,  d2 = (r w) . s   (one pass),   o_j = d2 - (r . au) d1 + (r . k) v_j,   s <- w s - au d1 + k v_j
+// - the numbers of "decay, remove, write, then read" with one pass over the state for both dot products.
+template <typename T, int R, int MAXT>
+__global__ void __launch_bounds__(MAXT) general_delta_kernel(const T* __restrict__ proj, int64_t proj_stride, int r_off,
+                                                             int k_off, int v_off, int a_off,
+                                                             const T* __restrict__ wp, int64_t w_stride,
+                                                             const float* __restrict__ w0, float rate, RecurArgs a) {
+  using L = Lay<R>;
+  extern __shared__ __align__(16) float sm[];
+  const int D = a.D, Dv = a.Dv, KS = a.KS, CW = a.CW, kTok = a.tok;
+  const int ROW = KS * L::SL;
+  float* su = sm;                       // [kTok][ROW] unit keys
+  float* sy = su + kTok * ROW;          // [kTok][ROW] r * w
+  float* sw = sy + kTok * ROW;          // [kTok][ROW] w
+  float* sa = sw + kTok * ROW;          // [kTok][ROW] sigmoid(a) * u
+  float* sk = sa + kTok * ROW;          // [kTok][ROW] k
+  float* sv = sk + kTok * ROW;          // [kTok][CW]
+  float* so = sv + kTok * CW;           // [kTok][CW]
+  float* sc = so + kTok * CW;           // [kTok][4]: r . au, r . k
+  float* part = sc + kTok * 4;          // [2][kTokMax]
+  float* sinv = part + 2 * kTokMax;     // [kTokMax]
+  const int h = blockIdx.x / a.VT, vt = blockIdx.x % a.VT, b = blockIdx.y;
+  int t0, n_new, start;
+  portion(a.g, b, t0, n_new, start);
+  if (n_new <= 0) return;               // the same for every CTA of the cluster
+  const int slot = a.g.slots[b];
+  const int c0 = vt * CW, ncol = min(CW, Dv - c0);
+  const int tid = threadIdx.x, j = tid / KS, ks = tid % KS;
+  const bool valid = j < ncol;
+  const int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
+  for (int i = tid; i < 5 * kTok * ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
+  float2 S[R / 2];
+  load_state<R>(S, a, slot, h, c0 + j, valid, ks, start > 0);
+  T pg[kPFG];
+  __syncthreads();
+  int stage = 0;
+  for (int j0 = 0; j0 < n_new; j0 += kTok, ++stage) {
+    const int n = min(kTok, n_new - j0);
+    for (int c = warp; c < n; c += warps) {   // a warp per token: unit key, rates, decays, the token's two scalars
+      const T* pr = proj + (int64_t)(t0 + j0 + c) * proj_stride + h * D;
+      const T* wr = wp + (int64_t)(t0 + j0 + c) * w_stride + h * D;
+      float kk = 0.f;
+      for (int d = lane; d < D; d += 32) {
+        const float kv = to_f<T>(pr[k_off + d]);
+        kk += kv * kv;
+      }
+      kk = warp_sum(kk);
+      const float ki = 1.0f / sqrtf(kk + 1e-6f);
+      float rau = 0.f, rk = 0.f;
+      for (int d = lane; d < D; d += 32) {
+        const float kv = to_f<T>(pr[k_off + d]), rv = to_f<T>(pr[r_off + d]);
+        const float u = kv * ki, au = sigmoid_f(to_f<T>(pr[a_off + d])) * u;
+        const float w = expf(-rate * sigmoid_f(to_f<T>(wr[d]) + w0[h * D + d]));
+        const int at = c * ROW + L::at(d);
+        su[at] = u;
+        sy[at] = rv * w;
+        sw[at] = w;
+        sa[at] = au;
+        sk[at] = kv;
+        rau = fmaf(rv, au, rau);
+        rk = fmaf(rv, kv, rk);
+      }
+      rau = warp_sum(rau);
+      rk = warp_sum(rk);
+      if (lane == 0) {
+        sc[c * 4 + 0] = rau;
+        sc[c * 4 + 1] = rk;
+      }
+    }
+    for (int i = tid; i < n * ncol; i += blockDim.x) {
+      const int c = i / ncol, d = i - c * ncol;
+      sv[c * CW + d] = to_f<T>(proj[(int64_t)(t0 + j0 + c) * proj_stride + v_off + h * Dv + c0 + d]);
+    }
+    prefetch_gates<T>(a, pg, h, c0, ncol, t0 + j0, n);
+    __syncthreads();
+    for (int c = 0; c < n; ++c) {
+      const float vj = valid ? sv[c * CW + j] : 0.f;
+      const float* base = sm + c * ROW + ks * L::SL;
+      const int plane = kTok * ROW;
+      float2 d1[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)}, d2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 u4 = *reinterpret_cast<const float4*>(base + r);
+        const float4 y4 = *reinterpret_cast<const float4*>(base + plane + r);
+        d1[0] = __ffma2_rn(S[r / 2], make_float2(u4.x, u4.y), d1[0]);
+        d1[1] = __ffma2_rn(S[r / 2 + 1], make_float2(u4.z, u4.w), d1[1]);
+        d2[0] = __ffma2_rn(S[r / 2], make_float2(y4.x, y4.y), d2[0]);
+        d2[1] = __ffma2_rn(S[r / 2 + 1], make_float2(y4.z, y4.w), d2[1]);
+      }
+      float d1s = (d1[0].x + d1[0].y) + (d1[1].x + d1[1].y), d2s = (d2[0].x + d2[0].y) + (d2[1].x + d2[1].y);
+      slice_sum2(d1s, d2s, KS);
+      if (ks == 0 && valid) so[c * CW + j] = fmaf(sc[c * 4 + 1], vj, fmaf(-sc[c * 4 + 0], d1s, d2s));
+      const float2 nd = make_float2(-d1s, -d1s), v2 = make_float2(vj, vj);
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 w4 = *reinterpret_cast<const float4*>(base + 2 * plane + r);
+        const float4 a4 = *reinterpret_cast<const float4*>(base + 3 * plane + r);
+        const float4 k4 = *reinterpret_cast<const float4*>(base + 4 * plane + r);
+        float2 x0 = __fmul2_rn(make_float2(w4.x, w4.y), S[r / 2]);
+        float2 x1 = __fmul2_rn(make_float2(w4.z, w4.w), S[r / 2 + 1]);
+        x0 = __ffma2_rn(make_float2(a4.x, a4.y), nd, x0);
+        x1 = __ffma2_rn(make_float2(a4.z, a4.w), nd, x1);
+        S[r / 2] = __ffma2_rn(make_float2(k4.x, k4.y), v2, x0);
+        S[r / 2 + 1] = __ffma2_rn(make_float2(k4.z, k4.w), v2, x1);
+      }
+    }
+    __syncthreads();
+    gated_unit_norm_rows<T>(a, so, part, sinv, stage, pg, h, c0, ncol, t0 + j0, n);
+    __syncthreads();
+  }
+  if (slot != a.reserved_slot) store_state<R>(S, a, slot, h, c0 + j, valid, ks);
+  if (a.VT > 1) cooperative_groups::this_cluster().sync();   // nobody leaves while its sums may still be read
+}
+
+// Matrix memory with exponential gates kept in range by a running maximum.  q, k, v, the gate and the two log-gate
+// logits (one per head) are columns of proj (model type) at q_off, k_off (+ h * D), v_off, gate_off (+ h * Dv),
+// i_off + h and f_off + h (biases already added).  i = cap tanh(z_i / cap), f = logsigmoid(cap tanh(z_f / cap));
+// m' = max(f + m, i), F = exp(f + m - m'), I = exp(i - m');  n <- F n + I k;  per value column j from the column s
+// before the token:  d = s . q,  o_j = (F d + I (k . q) v_j) / (max(|n . q|, exp(-m')) + 1e-6),  s <- F s + I v_j k.
+// q carries q_scale.  The running maximum m starts at 0, n and S at zero; nvec [slots, H, D] and mstate [slots, H]
+// hold n and m between steps.  The gates, the maximum and the normalizer of a stage's tokens are made by one warp that
+// walks the tokens in order (n in its registers); with several CTAs per head each makes them for itself.
+constexpr int kMaxNormRegs = kMaxKeyDim / 32;
+
+template <typename T, int R, int MAXT>
+__global__ void __launch_bounds__(MAXT) matrix_memory_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off,
+                                                             int k_off, int v_off, int i_off, int f_off, float cap,
+                                                             float q_scale, float* __restrict__ nvec,
+                                                             float* __restrict__ mstate, RecurArgs a) {
+  using L = Lay<R>;
+  extern __shared__ __align__(16) float sm[];
+  const int D = a.D, Dv = a.Dv, H = a.H, KS = a.KS, CW = a.CW, kTok = a.tok;
+  const int ROW = KS * L::SL;
+  float* sq = sm;                       // [kTok][ROW]
+  float* sk = sq + kTok * ROW;          // [kTok][ROW]
+  float* sv = sk + kTok * ROW;          // [kTok][CW]
+  float* so = sv + kTok * CW;           // [kTok][CW]
+  float* sc = so + kTok * CW;           // [kTok][4]: F, I, k . q, 1 / normalizer
+  float* part = sc + kTok * 4;          // [2][kTokMax]
+  float* sinv = part + 2 * kTokMax;     // [kTokMax]
+  const int h = blockIdx.x / a.VT, vt = blockIdx.x % a.VT, b = blockIdx.y;
+  int t0, n_new, start;
+  portion(a.g, b, t0, n_new, start);
+  if (n_new <= 0) return;               // the same for every CTA of the cluster
+  const int slot = a.g.slots[b];
+  const int c0 = vt * CW, ncol = min(CW, Dv - c0);
+  const int tid = threadIdx.x, j = tid / KS, ks = tid % KS;
+  const bool valid = j < ncol;
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < 2 * kTok * ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
+  float2 S[R / 2];
+  load_state<R>(S, a, slot, h, c0 + j, valid, ks, start > 0);
+  // warp 0: the normalizer vector (elements lane, lane + 32, ..) and the running maximum
+  float nv[kMaxNormRegs], mrun = 0.f;
+#pragma unroll
+  for (int e = 0; e < kMaxNormRegs; ++e) {
+    const int d = lane + 32 * e;
+    nv[e] = (warp == 0 && start > 0 && d < D) ? nvec[((int64_t)slot * H + h) * D + d] : 0.f;
+  }
+  if (warp == 0 && start > 0) mrun = mstate[(int64_t)slot * H + h];
+  T pg[kPFG];
+  __syncthreads();
+  int stage = 0;
+  for (int j0 = 0; j0 < n_new; j0 += kTok, ++stage) {
+    const int n = min(kTok, n_new - j0);
+    for (int i = tid; i < n * D; i += blockDim.x) {
+      const int c = i / D, d = i - c * D;
+      const T* pr = proj + (int64_t)(t0 + j0 + c) * proj_stride + h * D;
+      sq[c * ROW + L::at(d)] = to_f<T>(pr[q_off + d]) * q_scale;
+      sk[c * ROW + L::at(d)] = to_f<T>(pr[k_off + d]);
+    }
+    for (int i = tid; i < n * ncol; i += blockDim.x) {
+      const int c = i / ncol, d = i - c * ncol;
+      sv[c * CW + d] = to_f<T>(proj[(int64_t)(t0 + j0 + c) * proj_stride + v_off + h * Dv + c0 + d]);
+    }
+    for (int c = tid; c < n; c += blockDim.x) {   // the capped log gates
+      const T* pr = proj + (int64_t)(t0 + j0 + c) * proj_stride;
+      const float zi = cap * tanhf(to_f<T>(pr[i_off + h]) / cap), zf = cap * tanhf(to_f<T>(pr[f_off + h]) / cap);
+      sc[c * 4 + 0] = zf < -20.f ? zf : -log1pf(expf(-zf));   // logsigmoid
+      sc[c * 4 + 1] = zi;
+    }
+    prefetch_gates<T>(a, pg, h, c0, ncol, t0 + j0, n);
+    __syncthreads();
+    if (warp == 0) {
+      for (int c = 0; c < n; ++c) {
+        const float fl = sc[c * 4 + 0], il = sc[c * 4 + 1];
+        const float m_new = fmaxf(fl + mrun, il);
+        const float F = expf(fl + mrun - m_new), I = expf(il - m_new);
+        float nq = 0.f, kq = 0.f;
+#pragma unroll
+        for (int e = 0; e < kMaxNormRegs; ++e) {
+          const int d = lane + 32 * e;
+          if (d < D) {
+            const float kv = sk[c * ROW + L::at(d)], qv = sq[c * ROW + L::at(d)];
+            nv[e] = fmaf(F, nv[e], I * kv);
+            nq = fmaf(nv[e], qv, nq);
+            kq = fmaf(kv, qv, kq);
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          nq += __shfl_xor_sync(0xffffffffu, nq, o);
+          kq += __shfl_xor_sync(0xffffffffu, kq, o);
+        }
+        mrun = m_new;
+        __syncwarp();
+        if (lane == 0) {
+          sc[c * 4 + 0] = F;
+          sc[c * 4 + 1] = I;
+          sc[c * 4 + 2] = kq;
+          sc[c * 4 + 3] = 1.0f / (fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f);
+        }
+      }
+    }
+    __syncthreads();
+    for (int c = 0; c < n; ++c) {
+      const float vj = valid ? sv[c * CW + j] : 0.f;
+      const float F = sc[c * 4 + 0], I = sc[c * 4 + 1];
+      const float* qb = sq + c * ROW + ks * L::SL;
+      const float* kb = sk + c * ROW + ks * L::SL;
+      float2 d[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 F2 = make_float2(F, F), w2 = make_float2(I * vj, I * vj);
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(qb + r);
+        const float4 k4 = *reinterpret_cast<const float4*>(kb + r);
+        d[0] = __ffma2_rn(S[r / 2], make_float2(q4.x, q4.y), d[0]);
+        d[1] = __ffma2_rn(S[r / 2 + 1], make_float2(q4.z, q4.w), d[1]);
+        S[r / 2] = __ffma2_rn(make_float2(k4.x, k4.y), w2, __fmul2_rn(F2, S[r / 2]));
+        S[r / 2 + 1] = __ffma2_rn(make_float2(k4.z, k4.w), w2, __fmul2_rn(F2, S[r / 2 + 1]));
+      }
+      const float ds = slice_sum((d[0].x + d[0].y) + (d[1].x + d[1].y), KS);
+      if (ks == 0 && valid) so[c * CW + j] = fmaf(F, ds, I * sc[c * 4 + 2] * vj) * sc[c * 4 + 3];
+    }
+    __syncthreads();
+    gated_unit_norm_rows<T>(a, so, part, sinv, stage, pg, h, c0, ncol, t0 + j0, n);
+    __syncthreads();
+  }
+  if (slot != a.reserved_slot) {
+    store_state<R>(S, a, slot, h, c0 + j, valid, ks);
+    if (vt == 0 && warp == 0) {
+#pragma unroll
+      for (int e = 0; e < kMaxNormRegs; ++e) {
+        const int d = lane + 32 * e;
+        if (d < D) nvec[((int64_t)slot * H + h) * D + d] = nv[e];
+      }
+      if (lane == 0) mstate[(int64_t)slot * H + h] = mrun;
+    }
+  }
+  if (a.VT > 1) cooperative_groups::this_cluster().sync();   // nobody leaves while its sums may still be read
+}
+
 // How a (head, sequence) is laid out on CTAs and threads.
 struct RecurShape {
   int R, KS, VT, CW, threads, tok;
@@ -725,6 +988,32 @@ int launch_wkv(dim3 grid, const RecurShape& sh, cudaStream_t st, const void* r, 
   return CVLLM_OK;
 }
 
+template <typename T, int R, int MAXT>
+int launch_general_delta(dim3 grid, const RecurShape& sh, cudaStream_t st, const void* proj, int64_t proj_stride,
+                         int r_off, int k_off, int v_off, int a_off, const void* w_raw, int64_t w_stride,
+                         const float* w0, float rate, const RecurArgs& a) {
+  static std::atomic<uint64_t> attr{0};
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)general_delta_kernel<T, R, MAXT>, max_recur_smem<R>(5), attr));
+  CVLLM_CHECK_CUDA(launch_clustered(general_delta_kernel<T, R, MAXT>, grid, sh.threads, sh.smem(5), st, sh.VT,
+                                    static_cast<const T*>(proj), proj_stride, r_off, k_off, v_off, a_off,
+                                    static_cast<const T*>(w_raw), w_stride, w0, rate, a));
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+template <typename T, int R, int MAXT>
+int launch_matrix_memory(dim3 grid, const RecurShape& sh, cudaStream_t st, const void* proj, int64_t proj_stride,
+                         int q_off, int k_off, int v_off, int i_off, int f_off, float cap, float q_scale, float* nvec,
+                         float* mstate, const RecurArgs& a) {
+  static std::atomic<uint64_t> attr{0};
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)matrix_memory_kernel<T, R, MAXT>, max_recur_smem<R>(2), attr));
+  CVLLM_CHECK_CUDA(launch_clustered(matrix_memory_kernel<T, R, MAXT>, grid, sh.threads, sh.smem(2), st, sh.VT,
+                                    static_cast<const T*>(proj), proj_stride, q_off, k_off, v_off, i_off, f_off, cap,
+                                    q_scale, nvec, mstate, a));
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
 }  // namespace
 }  // namespace cvllm
 
@@ -824,4 +1113,58 @@ extern "C" int cvllm_wkv_scan(const void* r, int64_t r_stride, const void* k, in
   if (dtype == CVLLM_BF16) { CVLLM_RECUR_BY_R(CVLLM_WKV, __nv_bfloat16) }
   CVLLM_RECUR_BY_R(CVLLM_WKV, float)
 #undef CVLLM_WKV
+}
+
+extern "C" int cvllm_general_delta(const void* proj, int64_t proj_stride, int r_off, int k_off, int v_off, int a_off,
+                                   const void* w_raw, int64_t w_stride, const float* w0, float rate, float* state,
+                                   int gate_off, int gate_kind, const float* norm_w, int norm_head_stride, float eps,
+                                   const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                                   const int32_t* batch_mapping, int B, int max_new, void* out, int64_t out_stride,
+                                   int H, int D, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
+  CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && D > 0);
+  if (B == 0 || max_new == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(proj && w_raw && w0 && state && norm_w && batch_mapping && out && recur_dtype_ok(dtype));
+  CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
+  CVLLM_CHECK_SUPPORTED(D <= kMaxValueDim && H <= 65535 && B <= 65535);
+  auto st = static_cast<cudaStream_t>(stream);
+  RecurShape sh = recur_shape(D, D, H * B, max_new);
+  sh.pick_tok(max_new, 5);
+  CVLLM_CHECK_SUPPORTED(sh.threads > 0 && sh.threads <= 1024 && (int64_t)H * sh.VT <= 2147483647);
+  RecurArgs a{{cu_seqlens_q, seq_start, positions, batch_mapping}, state, proj, proj_stride, gate_off, norm_w,
+              norm_head_stride, eps, out, out_stride, H, D, D, reserved_slot, sh.KS, sh.VT, sh.CW, sh.tok, gate_kind};
+  const dim3 grid(H * sh.VT, B);
+#define CVLLM_GDELTA(T, RR, MT)                                                                                    \
+  launch_general_delta<T, RR, MT>(grid, sh, st, proj, proj_stride, r_off, k_off, v_off, a_off, w_raw, w_stride, w0, \
+                                  rate, a)
+  if (dtype == CVLLM_BF16) { CVLLM_RECUR_BY_R(CVLLM_GDELTA, __nv_bfloat16) }
+  CVLLM_RECUR_BY_R(CVLLM_GDELTA, float)
+#undef CVLLM_GDELTA
+}
+
+extern "C" int cvllm_matrix_memory(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_off, int i_off,
+                                   int f_off, float cap, float q_scale, float* state, float* nvec, float* mstate,
+                                   int gate_off, int gate_kind, const float* norm_w, int norm_head_stride, float eps,
+                                   const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                                   const int32_t* batch_mapping, int B, int max_new, void* out, int64_t out_stride,
+                                   int H, int D, int Dv, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  drop_stale_error();
+  CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && D > 0 && Dv > 0 && cap > 0.f);
+  if (B == 0 || max_new == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(proj && state && nvec && mstate && norm_w && batch_mapping && out && recur_dtype_ok(dtype));
+  CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
+  CVLLM_CHECK_SUPPORTED(D <= kMaxKeyDim && Dv <= kMaxValueDim && H <= 65535 && B <= 65535);
+  auto st = static_cast<cudaStream_t>(stream);
+  RecurShape sh = recur_shape(D, Dv, H * B, max_new);
+  sh.pick_tok(max_new, 2);
+  CVLLM_CHECK_SUPPORTED(sh.threads > 0 && sh.threads <= 1024 && (int64_t)H * sh.VT <= 2147483647);
+  RecurArgs a{{cu_seqlens_q, seq_start, positions, batch_mapping}, state, proj, proj_stride, gate_off, norm_w,
+              norm_head_stride, eps, out, out_stride, H, D, Dv, reserved_slot, sh.KS, sh.VT, sh.CW, sh.tok, gate_kind};
+  const dim3 grid(H * sh.VT, B);
+#define CVLLM_MMEM(T, RR, MT)                                                                                       \
+  launch_matrix_memory<T, RR, MT>(grid, sh, st, proj, proj_stride, q_off, k_off, v_off, i_off, f_off, cap, q_scale, \
+                                  nvec, mstate, a)
+  if (dtype == CVLLM_BF16) { CVLLM_RECUR_BY_R(CVLLM_MMEM, __nv_bfloat16) }
+  CVLLM_RECUR_BY_R(CVLLM_MMEM, float)
+#undef CVLLM_MMEM
 }

@@ -59,12 +59,14 @@ constexpr int kConvTokens = 8;   // tokens per CTA of the convolution
 
 // grid (token tiles, B, channel tiles), 128 threads = 128 channels.  x = columns x_off .. x_off + C of proj.
 // conv_state [slots, taps - 1, C]: entry s is the input at position start - (taps - 1) + s.
-template <typename T>
+// MODE 0: out = silu(bias + conv);  MODE 1: out = input + bias + conv (a convolution added to its own input, no
+// activation).  TO: the output's type (fp32, or the inputs' type).
+template <typename T, typename TO, int MODE>
 __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ proj, int64_t p_stride, int x_off, int C,
                                                           int taps, const float* __restrict__ w,
                                                           const float* __restrict__ bias,
                                                           const T* __restrict__ conv_state, StepGeom g,
-                                                          float* __restrict__ out, int64_t o_stride) {
+                                                          TO* __restrict__ out, int64_t o_stride) {
   const int b = blockIdx.y;
   int t0, n_new, start;
   portion(g, b, t0, n_new, start);
@@ -89,9 +91,10 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
         if (src >= 0) v = to_f<T>(proj[(int64_t)(t0 + src) * p_stride + x_off + ch]);
         else if (start + src >= 0) v = to_f<T>(st[(int64_t)(taps - 1 + src) * C]);   // start > 0: the slot's state
         acc = fmaf(wk[k], v, acc);
+        if (MODE == 1 && k == taps - 1) acc += v;
       }
     }
-    out[(int64_t)(t0 + j) * o_stride + ch] = silu_f(acc);
+    out[(int64_t)(t0 + j) * o_stride + ch] = from_f<TO>(MODE == 0 ? silu_f(acc) : acc);
   }
 }
 
@@ -99,12 +102,12 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
 // inputs in registers, so every input is read once.  grid (token runs, B, channel tiles), 128 threads.
 constexpr int kConvRun = 32;
 
-template <typename T, int TAPS>
+template <typename T, typename TO, int TAPS, int MODE>
 __global__ void __launch_bounds__(128) causal_conv_run_kernel(const T* __restrict__ proj, int64_t p_stride, int x_off,
                                                               int C, const float* __restrict__ w,
                                                               const float* __restrict__ bias,
                                                               const T* __restrict__ conv_state, StepGeom g,
-                                                              float* __restrict__ out, int64_t o_stride) {
+                                                              TO* __restrict__ out, int64_t o_stride) {
   const int b = blockIdx.y;
   int t0, n_new, start;
   portion(g, b, t0, n_new, start);
@@ -133,7 +136,8 @@ __global__ void __launch_bounds__(128) causal_conv_run_kernel(const T* __restric
     float acc = bv;
 #pragma unroll
     for (int k = 0; k < TAPS; ++k) acc = fmaf(wk[k], win[k], acc);
-    out[(int64_t)(t0 + j) * o_stride + ch] = silu_f(acc);
+    if (MODE == 1) acc += win[TAPS - 1];
+    out[(int64_t)(t0 + j) * o_stride + ch] = from_f<TO>(MODE == 0 ? silu_f(acc) : acc);
 #pragma unroll
     for (int k = 0; k < TAPS - 1; ++k) win[k] = win[k + 1];
   }
@@ -473,6 +477,104 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __re
   for (int i = threadIdx.x; i < part; i += 128) out[t * o_stride + c0 + i] = from_f<T>(vals[i] * inv * w[c0 + i]);
 }
 
+// Selective scan with a decay per (channel, state channel) and a step size per channel:
+//     dt_t[c] = softplus(dt_raw_t[c] + dt_bias[c])      S_t[c, n] = exp(dt_t[c] A[c, n]) S_(t-1)[c, n] + dt_t[c] x_t[c] B_t[n]
+//     y_t[c]  = sum_n S_t[c, n] C_t[n] + D[c] x_t[c]     out_t[c] = y_t[c] silu(z_t[c])
+// with A = -exp(A_log) [channels, N].  grid (channel tiles, B), CT * NS threads: thread (pl, s) keeps the kSelNPT state
+// channels s * kSelNPT .. of channel c0 + pl in registers over the portion's tokens (NS a power of two,
+// NS * kSelNPT >= N); a token's B and C rows, and the tile's step sizes and inputs, are staged kSelTokens tokens at a
+// time.  x, dt_raw, the B | C columns and z are stored projections (model type); the rest is fp32.
+constexpr int kSelTokens = 16;
+constexpr int kSelNPT = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict__ x, int64_t x_stride,
+                                                             const T* __restrict__ dt_raw, int64_t dt_stride,
+                                                             const float* __restrict__ dt_bias,
+                                                             const T* __restrict__ bc, int64_t bc_stride, int b_off,
+                                                             int c_off, const float* __restrict__ A_log,
+                                                             const float* __restrict__ Dp, const T* __restrict__ z,
+                                                             int64_t z_stride, int z_off, float* __restrict__ state,
+                                                             StepGeom g, T* __restrict__ out, int64_t o_stride,
+                                                             int inner, int N, int NS, int CT, int reserved_slot) {
+  extern __shared__ __align__(16) float sm[];
+  const int NSP = NS * kSelNPT;
+  float* sB = sm;                              // [kSelTokens][NSP]
+  float* sC = sB + kSelTokens * NSP;           // [kSelTokens][NSP]
+  float* sdt = sC + kSelTokens * NSP;          // [kSelTokens][CT]
+  float* sx = sdt + kSelTokens * CT;           // [kSelTokens][CT]
+  float* sy = sx + kSelTokens * CT;            // [kSelTokens][CT]
+  const int b = blockIdx.y, c0 = blockIdx.x * CT;
+  int t0, n_new, start;
+  portion(g, b, t0, n_new, start);
+  if (n_new <= 0) return;
+  const int slot = g.slots[b];
+  const int tid = threadIdx.x, nthr = blockDim.x, s = tid & (NS - 1), pl = tid / NS;
+  const int ch = c0 + pl;
+  const bool live = ch < inner;
+  if (slot == reserved_slot) {
+    for (int i = tid; i < n_new * CT; i += nthr) {
+      const int j = i / CT, c = i - j * CT;
+      if (c0 + c < inner) out[(int64_t)(t0 + j) * o_stride + c0 + c] = from_f<T>(0.f);
+    }
+    return;
+  }
+  float S[kSelNPT], A[kSelNPT];
+  float* srow = state + ((int64_t)slot * inner + ch) * N + s * kSelNPT;
+#pragma unroll
+  for (int e = 0; e < kSelNPT; ++e) {
+    const bool in = live && s * kSelNPT + e < N;
+    A[e] = in ? -expf(A_log[(int64_t)ch * N + s * kSelNPT + e]) : 0.f;
+    S[e] = (in && start > 0) ? srow[e] : 0.f;
+  }
+  const float dsk = live ? Dp[ch] : 0.f;
+  for (int j0 = 0; j0 < n_new; j0 += kSelTokens) {
+    const int n = min(kSelTokens, n_new - j0);
+    for (int i = tid; i < n * NSP; i += nthr) {
+      const int j = i / NSP, nn = i - j * NSP;
+      const T* row = bc + (int64_t)(t0 + j0 + j) * bc_stride;
+      sB[i] = nn < N ? to_f<T>(row[b_off + nn]) : 0.f;
+      sC[i] = nn < N ? to_f<T>(row[c_off + nn]) : 0.f;
+    }
+    for (int i = tid; i < n * CT; i += nthr) {
+      const int j = i / CT, c = i - j * CT;
+      const bool in = c0 + c < inner;
+      const int64_t t = t0 + j0 + j;
+      sdt[i] = in ? softplus_f(to_f<T>(dt_raw[t * dt_stride + c0 + c]) + dt_bias[c0 + c]) : 0.f;
+      sx[i] = in ? to_f<T>(x[t * x_stride + c0 + c]) : 0.f;
+    }
+    __syncthreads();
+    for (int j = 0; j < n; ++j) {
+      const float dt = sdt[j * CT + pl], xv = sx[j * CT + pl];
+      const float dx = dt * xv;
+      const float* Bj = sB + j * NSP + s * kSelNPT;
+      const float* Cj = sC + j * NSP + s * kSelNPT;
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < kSelNPT; ++e) {
+        S[e] = fmaf(expf(dt * A[e]), S[e], dx * Bj[e]);
+        acc = fmaf(S[e], Cj[e], acc);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        if (o < NS) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (s == 0) sy[j * CT + pl] = fmaf(dsk, xv, acc);
+    }
+    __syncthreads();
+    for (int i = tid; i < n * CT; i += nthr) {
+      const int j = i / CT, c = i - j * CT;
+      if (c0 + c < inner) {
+        const int64_t t = t0 + j0 + j;
+        out[t * o_stride + c0 + c] = from_f<T>(sy[i] * silu_f(to_f<T>(z[t * z_stride + z_off + c0 + c])));
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int e = 0; e < kSelNPT; ++e)
+    if (live && s * kSelNPT + e < N) srow[e] = S[e];
+}
+
 // state channels per thread: 8 (twice the threads, for the latencies of a sequential recurrence) up to N = 256, else 16
 int scan_npt(int N) { return N <= 256 ? 8 : 16; }
 
@@ -517,47 +619,67 @@ using namespace cvllm;
 
 static int ssm_dtype_ok(int dtype) { return dtype == CVLLM_BF16 || dtype == CVLLM_F32; }
 
+namespace {
+
+template <typename T, typename TO, int MODE>
+int launch_conv(const void* proj, int64_t proj_stride, int x_off, int channels, int taps, const float* weight,
+                const float* bias, const void* conv_state, const StepGeom& g, int B, int max_new, void* out,
+                int64_t out_stride, cudaStream_t st) {
+  const T* in = static_cast<const T*>(proj);
+  const T* cs = static_cast<const T*>(conv_state);
+  TO* o = static_cast<TO*>(out);
+  if (taps >= 2 && taps <= 4) {
+    const dim3 rgrid(cdiv(max_new, kConvRun), B, cdiv(channels, 128));
+    if (taps == 2)
+      causal_conv_run_kernel<T, TO, 2, MODE><<<rgrid, 128, 0, st>>>(in, proj_stride, x_off, channels, weight, bias, cs, g, o, out_stride);
+    else if (taps == 3)
+      causal_conv_run_kernel<T, TO, 3, MODE><<<rgrid, 128, 0, st>>>(in, proj_stride, x_off, channels, weight, bias, cs, g, o, out_stride);
+    else
+      causal_conv_run_kernel<T, TO, 4, MODE><<<rgrid, 128, 0, st>>>(in, proj_stride, x_off, channels, weight, bias, cs, g, o, out_stride);
+  } else {
+    const dim3 grid(cdiv(max_new, kConvTokens), B, cdiv(channels, 128));
+    causal_conv_kernel<T, TO, MODE><<<grid, 128, 0, st>>>(in, proj_stride, x_off, channels, taps, weight, bias, cs, g, o, out_stride);
+  }
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+}  // namespace
+
 extern "C" int cvllm_causal_conv(const void* proj, int64_t proj_stride, int x_off, int channels, int taps,
                                  const float* weight, const float* bias, const void* conv_state,
                                  const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
                                  const int32_t* batch_mapping, int B, int max_new, float* out, int64_t out_stride,
                                  int dtype, cvllm_stream_t stream) {
-  CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && channels > 0 && taps >= 1);
+  return cvllm_causal_conv_mode(proj, proj_stride, x_off, channels, taps, weight, bias, conv_state, cu_seqlens_q,
+                                seq_start, positions, batch_mapping, B, max_new, out, out_stride, CVLLM_F32, 0, dtype,
+                                stream);
+}
+
+extern "C" int cvllm_causal_conv_mode(const void* proj, int64_t proj_stride, int x_off, int channels, int taps,
+                                      const float* weight, const float* bias, const void* conv_state,
+                                      const int32_t* cu_seqlens_q, const int32_t* seq_start,
+                                      const int32_t* positions, const int32_t* batch_mapping, int B, int max_new,
+                                      void* out, int64_t out_stride, int out_dtype, int mode, int dtype,
+                                      cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && channels > 0 && taps >= 1 && (mode == 0 || mode == 1));
   if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(proj && weight && out && batch_mapping && ssm_dtype_ok(dtype) && (taps == 1 || conv_state));
+  CVLLM_CHECK_ARG(out_dtype == CVLLM_F32 || out_dtype == dtype);
   CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
   CVLLM_CHECK_SUPPORTED(taps <= kMaxTaps && B <= 65535 && cdiv(channels, 128) <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
   const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
-  if (taps >= 2 && taps <= 4) {
-    const dim3 rgrid(cdiv(max_new, kConvRun), B, cdiv(channels, 128));
-#define CVLLM_CONV(T, TAPS)                                                                                     \
-  causal_conv_run_kernel<T, TAPS><<<rgrid, 128, 0, st>>>(static_cast<const T*>(proj), proj_stride, x_off, channels, \
-                                                         weight, bias, static_cast<const T*>(conv_state), g, out,  \
-                                                         out_stride)
-    if (dtype == CVLLM_BF16) {
-      if (taps == 2) CVLLM_CONV(__nv_bfloat16, 2); else if (taps == 3) CVLLM_CONV(__nv_bfloat16, 3);
-      else CVLLM_CONV(__nv_bfloat16, 4);
-    } else {
-      if (taps == 2) CVLLM_CONV(float, 2); else if (taps == 3) CVLLM_CONV(float, 3);
-      else CVLLM_CONV(float, 4);
-    }
-#undef CVLLM_CONV
-    CVLLM_CHECK_LAUNCH();
-    return CVLLM_OK;
+#define CVLLM_CONV(T, TO, MODE) \
+  return launch_conv<T, TO, MODE>(proj, proj_stride, x_off, channels, taps, weight, bias, conv_state, g, B, max_new, out, out_stride, st)
+  if (dtype == CVLLM_BF16) {
+    if (out_dtype == CVLLM_F32) { if (mode == 0) CVLLM_CONV(__nv_bfloat16, float, 0); CVLLM_CONV(__nv_bfloat16, float, 1); }
+    if (mode == 0) CVLLM_CONV(__nv_bfloat16, __nv_bfloat16, 0);
+    CVLLM_CONV(__nv_bfloat16, __nv_bfloat16, 1);
   }
-  const dim3 grid(cdiv(max_new, kConvTokens), B, cdiv(channels, 128));
-  if (dtype == CVLLM_BF16)
-    causal_conv_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(proj), proj_stride, x_off,
-                                                            channels, taps, weight, bias,
-                                                            static_cast<const __nv_bfloat16*>(conv_state), g, out,
-                                                            out_stride);
-  else
-    causal_conv_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(proj), proj_stride, x_off, channels, taps,
-                                                    weight, bias, static_cast<const float*>(conv_state), g, out,
-                                                    out_stride);
-  CVLLM_CHECK_LAUNCH();
-  return CVLLM_OK;
+  if (mode == 0) CVLLM_CONV(float, float, 0);
+  CVLLM_CONV(float, float, 1);
+#undef CVLLM_CONV
 }
 
 extern "C" int cvllm_conv_state_update(const void* proj, int64_t proj_stride, int x_off, int channels, int taps,
@@ -670,6 +792,45 @@ extern "C" int cvllm_gated_group_norm(const float* y, int64_t y_stride, const vo
   else
     gated_group_norm_kernel<float><<<grid, 128, smem, st>>>(y, y_stride, static_cast<const float*>(z), z_stride, weight,
                                                             eps, static_cast<float*>(out), out_stride, part);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_selective_scan(const void* x, int64_t x_stride, const void* dt_raw, int64_t dt_stride,
+                                    const float* dt_bias, const void* bc, int64_t bc_stride, int b_off, int c_off,
+                                    const float* A_log, const float* D, const void* z, int64_t z_stride, int z_off,
+                                    float* state, const int32_t* cu_seqlens_q, const int32_t* seq_start,
+                                    const int32_t* positions, const int32_t* batch_mapping, int B, int max_new,
+                                    void* out, int64_t out_stride, int inner, int N, int reserved_slot, int dtype,
+                                    cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && inner > 0 && N > 0);
+  if (B == 0 || max_new == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(x && dt_raw && dt_bias && bc && A_log && D && z && state && batch_mapping && out &&
+                  ssm_dtype_ok(dtype));
+  CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
+  int NS = 1;
+  while (NS * kSelNPT < N) NS <<= 1;
+  CVLLM_CHECK_SUPPORTED(NS <= 32 && B <= 65535);
+  // channels per CTA: 256 threads while that still gives two CTAs per SM, down to 64 threads
+  int threads = 256;
+  while (threads > 64 && threads / NS > 1 && (int64_t)B * cdiv(inner, threads / NS) < 2 * (int64_t)sm_count()) threads >>= 1;
+  if (threads < NS) threads = NS;
+  if (threads < 32) threads = 32;
+  const int CT = threads / NS;
+  auto st = static_cast<cudaStream_t>(stream);
+  const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
+  const dim3 grid(cdiv(inner, CT), B);
+  const size_t smem = sizeof(float) * (size_t)kSelTokens * (2 * NS * kSelNPT + 3 * CT);
+  if (dtype == CVLLM_BF16)
+    selective_scan_kernel<__nv_bfloat16><<<grid, threads, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(x), x_stride, static_cast<const __nv_bfloat16*>(dt_raw), dt_stride, dt_bias,
+        static_cast<const __nv_bfloat16*>(bc), bc_stride, b_off, c_off, A_log, D, static_cast<const __nv_bfloat16*>(z),
+        z_stride, z_off, state, g, static_cast<__nv_bfloat16*>(out), out_stride, inner, N, NS, CT, reserved_slot);
+  else
+    selective_scan_kernel<float><<<grid, threads, smem, st>>>(
+        static_cast<const float*>(x), x_stride, static_cast<const float*>(dt_raw), dt_stride, dt_bias,
+        static_cast<const float*>(bc), bc_stride, b_off, c_off, A_log, D, static_cast<const float*>(z), z_stride,
+        z_off, state, g, static_cast<float*>(out), out_stride, inner, N, NS, CT, reserved_slot);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
 }

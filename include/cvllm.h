@@ -520,6 +520,26 @@ int cvllm_bias_attn_decode(const void* q, const void* k_cache, const void* v_cac
                            int splits, float* workspace, size_t workspace_bytes, int64_t v_stride, int dtype,
                            cvllm_stream_t stream);
 
+/* The same two with a sliding window and a learned bias per distance beside the linear bias and the chunk mask:
+ * a query sees the keys at distances 0 .. window - 1 (window 0: no limit), and the score of the key at distance n
+ * gets dist_bias[min(n, dist_rows - 1), h] (fp32 [dist_rows, H]; NULL = none), unscaled.  The caller makes the
+ * table, so any rule from distance to bias (buckets of a smaller learned table) is served.  These shapes run on the
+ * mma.sync and fp32 FMA kernels. */
+int cvllm_bias_attn_varlen_dist(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
+                                int64_t table_stride_slot, int64_t table_stride_head, int page_size,
+                                const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* batch_mapping,
+                                const float* slopes, int chunk, int window, const float* dist_bias, int dist_rows,
+                                int sink, const float* sink_logits, float scale, void* out, int B, int max_new, int H,
+                                int G, int D, int Dv, int total_tokens, int64_t cache_rows, int pages_per_head,
+                                int64_t v_stride, int dtype, cvllm_stream_t stream);
+int cvllm_bias_attn_decode_dist(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
+                                int64_t table_stride_slot, int64_t table_stride_head, int page_size,
+                                const int32_t* positions, const int32_t* batch_mapping, const float* slopes, int chunk,
+                                int window, const float* dist_bias, int dist_rows, int sink, const float* sink_logits,
+                                float scale, void* out, int B, int H, int G, int D, int Dv, int reserved_slot,
+                                int splits, float* workspace, size_t workspace_bytes, int64_t v_stride, int dtype,
+                                cvllm_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Latent attention (csrc/latent_attn.cu): the steps around attention in the latent space.  The cache row of a token
  * is [c | k_rot] (kv_rank + rot_dim numbers, one key/value head).  inv_freq: rot_dim / 2 doubles, base ** (-2 i / rot_dim).
@@ -542,6 +562,31 @@ int cvllm_latent_q_rope(const void* q, int64_t q_stride, int H, int D, int rot_d
                         const int32_t* positions, void* q_full, int64_t full_stride, int full_head, int off, int T,
                         int dtype, cvllm_stream_t stream);
 
+/* Gated residual sum fused with the next RMS norm, one launch on a 32-bit residual stream [rows, width]:
+ *   resid += sigmoid(gate) * y   (y, gate [rows, width] bfloat16 or float32; both NULL: no sum)
+ *   out = resid / sqrt(mean(resid^2) + eps) * w   (out NULL: the sum alone).  Sum and statistics are fp32. */
+int cvllm_gated_residual_norm(const void* y, int64_t y_stride, int y_dtype, const void* gate, int64_t g_stride,
+                              int g_dtype, float* resid, int64_t r_stride, const float* w, void* out, int64_t o_stride,
+                              int out_dtype, int rows, int width, float eps, cvllm_stream_t stream);
+
+/* out = scale * (a / rms(a) * wa + b / rms(b) * wb) per row, rms(v) = sqrt(mean(v^2) + eps); weights fp32. */
+int cvllm_dual_norm_blend(const void* a, int64_t a_stride, const float* wa, const void* b, int64_t b_stride,
+                          const float* wb, void* out, int64_t o_stride, int rows, int width, float eps, float scale,
+                          int dtype, cvllm_stream_t stream);
+
+/* out = act(x) element by element; kind 0: relu(x)^2. */
+int cvllm_unary_act(const void* x, int64_t x_stride, void* out, int64_t o_stride, int64_t rows, int F, int kind,
+                    int dtype, cvllm_stream_t stream);
+
+/* out = cap * tanh(x / cap), fp32 out (logit soft cap). */
+int cvllm_softcap(const void* x, int64_t x_stride, float* out, int64_t o_stride, int64_t rows, int F, float cap,
+                  int dtype, cvllm_stream_t stream);
+
+/* out[p, :] = x[pair / top, :] * scale[pair] with pair = perm ? perm[p] : p: rows of (token, choice) pairs multiplied
+ * by their routing weight on the way into the experts. */
+int cvllm_scaled_rows(const void* x, int64_t x_stride, const int64_t* perm, const float* scale, int top, void* out,
+                      int64_t pairs, int width, int dtype, cvllm_stream_t stream);
+
 /* out[t, c] = x[t, c] * sigmoid(gate[t, c]) */
 int cvllm_sigmoid_gate(const void* x, int64_t x_stride, const void* gate, int64_t g_stride, void* out,
                        int64_t o_stride, int64_t rows, int width, int dtype, cvllm_stream_t stream);
@@ -558,6 +603,25 @@ int cvllm_causal_conv(const void* proj, int64_t proj_stride, int x_off, int chan
                       const float* bias, const void* conv_state, const int32_t* cu_seqlens_q,
                       const int32_t* seq_start, const int32_t* positions, const int32_t* batch_mapping, int B,
                       int max_new, float* out, int64_t out_stride, int dtype, cvllm_stream_t stream);
+
+/* The same with a choice of what comes out: mode 0 silu(bias + conv), mode 1 input + bias + conv (the convolution
+ * added to its own input, no activation); out_dtype CVLLM_F32 or the inputs' dtype. */
+int cvllm_causal_conv_mode(const void* proj, int64_t proj_stride, int x_off, int channels, int taps,
+                           const float* weight, const float* bias, const void* conv_state,
+                           const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                           const int32_t* batch_mapping, int B, int max_new, void* out, int64_t out_stride,
+                           int out_dtype, int mode, int dtype, cvllm_stream_t stream);
+
+/* Selective scan with a decay per (channel, state channel): x, dt_raw [T, inner], the columns B | C of bc (N each, at
+ * b_off / c_off) and z (at z_off) are stored projections of the model type;
+ *   dt = softplus(dt_raw + dt_bias[c]);  S[c, n] <- exp(-exp(A_log[c, n]) dt) S[c, n] + dt x[c] B[n];
+ *   out[c] = (sum_n S[c, n] C[n] + D[c] x[c]) * silu(z[c]).   state fp32 [slots, inner, N]. */
+int cvllm_selective_scan(const void* x, int64_t x_stride, const void* dt_raw, int64_t dt_stride, const float* dt_bias,
+                         const void* bc, int64_t bc_stride, int b_off, int c_off, const float* A_log, const float* D,
+                         const void* z, int64_t z_stride, int z_off, float* state, const int32_t* cu_seqlens_q,
+                         const int32_t* seq_start, const int32_t* positions, const int32_t* batch_mapping, int B,
+                         int max_new, void* out, int64_t out_stride, int inner, int N, int reserved_slot, int dtype,
+                         cvllm_stream_t stream);
 
 /* conv_state of every sequence of the step := its last taps - 1 inputs (after cvllm_causal_conv has read the old one). */
 int cvllm_conv_state_update(const void* proj, int64_t proj_stride, int x_off, int channels, int taps, void* conv_state,
@@ -618,6 +682,31 @@ int cvllm_wkv_scan(const void* r, int64_t r_stride, const void* k, int64_t k_str
                    float eps, const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
                    const int32_t* batch_mapping, int B, int max_new, void* out, int64_t out_stride, int H, int D,
                    int reserved_slot, int dtype, cvllm_stream_t stream);
+
+/* General delta rule: r, k, v, removal-rate logits and the gate are columns of proj (model type) at r_off, k_off,
+ * v_off, a_off, gate_off (+ h * D); w_raw rows of H * D decay logits: w = exp(-rate * sigmoid(w_raw + w0)).  With the
+ * unit key u = k / sqrt(sum k^2 + 1e-6) and a = sigmoid(.) per head and key channel
+ *   S <- diag(w) S - (a u)(u^T S) + k v^T   (both terms on the old S);   o = S^T r.   Dv = D.
+ * gate_kind 0: the output is multiplied by silu(gate), 1: by sigmoid(gate). */
+int cvllm_general_delta(const void* proj, int64_t proj_stride, int r_off, int k_off, int v_off, int a_off,
+                        const void* w_raw, int64_t w_stride, const float* w0, float rate, float* state, int gate_off,
+                        int gate_kind, const float* norm_w, int norm_head_stride, float eps,
+                        const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                        const int32_t* batch_mapping, int B, int max_new, void* out, int64_t out_stride, int H, int D,
+                        int reserved_slot, int dtype, cvllm_stream_t stream);
+
+/* Matrix memory with exponential gates: q, k (H x D), v, gate (H x Dv) and one input-gate and one forget-gate logit
+ * per head are columns of proj at q_off, k_off, v_off, gate_off, i_off + h, f_off + h.  i = cap tanh(z_i / cap),
+ * f = logsigmoid(cap tanh(z_f / cap)); with the running maximum m (starts at 0): m' = max(f + m, i),
+ *   S <- exp(f + m - m') S + exp(i - m') k v^T,  n likewise with k alone,
+ *   o = S^T q / (max(|n . q|, exp(-m')) + 1e-6),   q times q_scale.
+ * state [slots, H, Dv, D], nvec [slots, H, D], mstate [slots, H], all fp32. */
+int cvllm_matrix_memory(const void* proj, int64_t proj_stride, int q_off, int k_off, int v_off, int i_off, int f_off,
+                        float cap, float q_scale, float* state, float* nvec, float* mstate, int gate_off,
+                        int gate_kind, const float* norm_w, int norm_head_stride, float eps,
+                        const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                        const int32_t* batch_mapping, int B, int max_new, void* out, int64_t out_stride, int H, int D,
+                        int Dv, int reserved_slot, int dtype, cvllm_stream_t stream);
 
 #ifdef __cplusplus
 }
