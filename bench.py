@@ -743,7 +743,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="only the headline step (for ncu runs)")
     ap.add_argument("--only-cfg5", action="store_true", help=argparse.SUPPRESS)
-    ap.add_argument("--arch", default=None, choices=["movolorn", "batasun", "fafelix"],
+    ap.add_argument("--arch", default=None, choices=["movolorn", "batasun", "fafelix", "nununex"],
                     help="instead of the headline workload: prefill / decode throughput of this model design beside "
                          "the closest existing model at equal size, and its kernels against the measured peaks")
     ap.add_argument("--arch-sizes", default="1b-like,8b-like", help="with --arch: comma-separated size names")
@@ -755,6 +755,8 @@ def main():
             from compactor_vllm.benchmarks import batasun_compare as arch_compare
         elif args.arch == "fafelix":
             from compactor_vllm.benchmarks import fafelix_compare as arch_compare
+        elif args.arch == "nununex":
+            from compactor_vllm.benchmarks import nununex_compare as arch_compare
         else:
             from compactor_vllm.benchmarks import arch_compare
 
