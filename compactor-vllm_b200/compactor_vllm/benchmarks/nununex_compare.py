@@ -170,8 +170,8 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
     rows[-1]["GFLOPs_fp32"] = round(10.0 * Dg * Dg * Hg * L / rows[-1]["ms"] / 1e6, 1)
     add("general_delta (decode, 8 sequences: state read + written)", timed(lambda: gdelta(dec, slotsB, B, 1)),
         nbytes=2 * 4 * B * Hg * Dg * Dg, like="wkv_scan (decode)")
-    # --- matrix memory: 16 heads of 128 x 128
-    Hm, Dm = W // 2 // MEMORY_DIM, MEMORY_DIM
+    # --- matrix memory: 32 heads of 128 x 128 (the delta rule's shape in the Fafelix comparison)
+    Hm, Dm = W // MEMORY_DIM, MEMORY_DIM
     mcols = torch.randn(L, 4 * Hm * Dm + 2 * Hm, device=dev).to(bf)
     mstate = torch.zeros(B + 1, Hm, Dm, Dm, device=dev)
     nvec, mrun = torch.zeros(B + 1, Hm, Dm, device=dev), torch.zeros(B + 1, Hm, device=dev)

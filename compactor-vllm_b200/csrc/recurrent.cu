@@ -729,10 +729,11 @@ __global__ void __launch_bounds__(MAXT) general_delta_kernel(const T* __restrict
 // m' = max(f + m, i), F = exp(f + m - m'), I = exp(i - m');  n <- F n + I k;  per value column j from the column s
 // before the token:  d = s . q,  o_j = (F d + I (k . q) v_j) / (max(|n . q|, exp(-m')) + 1e-6),  s <- F s + I v_j k.
 // q carries q_scale.  The running maximum m starts at 0, n and S at zero; nvec [slots, H, D] and mstate [slots, H]
-// hold n and m between steps.  The gates, the maximum and the normalizer of a stage's tokens are made by one warp that
-// walks the tokens in order (n in its registers); with several CTAs per head each makes them for itself.
-constexpr int kMaxNormRegs = kMaxKeyDim / 32;
-
+// hold n and m between steps.  The normalizer n is the state's column of a value that is always 1: every CTA keeps it
+// as one more column (threads j == ncol) and gets n . q from the same pass as its read-outs; the division waits for
+// the end of the stage.  The maximum and the two gates are a scalar recurrence over the tokens: the CTA's LAST warp
+// has no columns and walks it for the NEXT stage while the other warps run the current stage's tokens; a stage's
+// inputs are loaded into registers one stage ahead, as in the delta rule.
 template <typename T, int R, int MAXT>
 __global__ void __launch_bounds__(MAXT) matrix_memory_kernel(const T* __restrict__ proj, int64_t proj_stride, int q_off,
                                                              int k_off, int v_off, int i_off, int f_off, float cap,
@@ -746,9 +747,11 @@ __global__ void __launch_bounds__(MAXT) matrix_memory_kernel(const T* __restrict
   float* sk = sq + kTok * ROW;          // [kTok][ROW]
   float* sv = sk + kTok * ROW;          // [kTok][CW]
   float* so = sv + kTok * CW;           // [kTok][CW]
-  float* sc = so + kTok * CW;           // [kTok][4]: F, I, k . q, 1 / normalizer
-  float* part = sc + kTok * 4;          // [2][kTokMax]
+  float* skq = so + kTok * CW;          // [kTok][4]: k . q of the token (first of four)
+  float* part = skq + kTok * 4;         // [2][kTokMax]
   float* sinv = part + 2 * kTokMax;     // [kTokMax]
+  float* sden = sinv + kTokMax;         // [kTokMax]: n . q of the token
+  float* sg = sden + kTokMax;           // [2][kTokMax][4]: per stage parity: F, I, exp(-m') (before the walk: f, i)
   const int h = blockIdx.x / a.VT, vt = blockIdx.x % a.VT, b = blockIdx.y;
   int t0, n_new, start;
   portion(a.g, b, t0, n_new, start);
@@ -756,92 +759,132 @@ __global__ void __launch_bounds__(MAXT) matrix_memory_kernel(const T* __restrict
   const int slot = a.g.slots[b];
   const int c0 = vt * CW, ncol = min(CW, Dv - c0);
   const int tid = threadIdx.x, j = tid / KS, ks = tid % KS;
-  const bool valid = j < ncol;
-  const int warp = tid >> 5, lane = tid & 31;
+  const int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
+  const int workers = warps - 1;        // warps with columns; the last warp walks the gates
+  const bool walker_warp = warp == workers;
+  const bool valid = j < ncol && !walker_warp, is_n = j == ncol && !walker_warp;
+  const int wthreads = workers * 32;
   for (int i = tid; i < 2 * kTok * ROW; i += blockDim.x) sm[i] = 0.f;   // pads and rows beyond D stay zero
   float2 S[R / 2];
   load_state<R>(S, a, slot, h, c0 + j, valid, ks, start > 0);
-  // warp 0: the normalizer vector (elements lane, lane + 32, ..) and the running maximum
-  float nv[kMaxNormRegs], mrun = 0.f;
+  if (is_n) {
+    const float* src = nvec + ((int64_t)slot * H + h) * D;
 #pragma unroll
-  for (int e = 0; e < kMaxNormRegs; ++e) {
-    const int d = lane + 32 * e;
-    nv[e] = (warp == 0 && start > 0 && d < D) ? nvec[((int64_t)slot * H + h) * D + d] : 0.f;
+    for (int r = 0; r < R; r += 2) {
+      const int i = ks * R + r;
+      S[r / 2] = make_float2((start > 0 && i < D) ? src[i] : 0.f, (start > 0 && i + 1 < D) ? src[i + 1] : 0.f);
+    }
   }
-  if (warp == 0 && start > 0) mrun = mstate[(int64_t)slot * H + h];
-  T pg[kPFG];
+  float mrun = (walker_warp && lane == 0 && start > 0) ? mstate[(int64_t)slot * H + h] : 0.f;
+  // the capped log gates of a stage's tokens (any thread may make them), then the walk by one lane
+  auto gates = [&](int j0n, float* dst) {
+    const int nn = min(kTok, n_new - j0n);
+    for (int c = tid; c < nn; c += blockDim.x) {
+      const T* pr = proj + (int64_t)(t0 + j0n + c) * proj_stride;
+      const float zi = cap * tanhf(to_f<T>(pr[i_off + h]) / cap), zf = cap * tanhf(to_f<T>(pr[f_off + h]) / cap);
+      dst[c * 4 + 0] = zf < -20.f ? zf : -log1pf(expf(-zf));   // logsigmoid
+      dst[c * 4 + 1] = zi;
+    }
+  };
+  auto walk = [&](int j0n, float* dst) {
+    const int nn = min(kTok, n_new - j0n);
+    for (int c = 0; c < nn; ++c) {
+      const float fl = dst[c * 4 + 0], il = dst[c * 4 + 1];
+      const float m_new = fmaxf(fl + mrun, il);
+      dst[c * 4 + 0] = expf(fl + mrun - m_new);
+      dst[c * 4 + 1] = expf(il - m_new);
+      dst[c * 4 + 2] = expf(-m_new);
+      mrun = m_new;
+    }
+  };
+  T pq[kPF], pk[kPF], pv[kPFG], pg[kPFG];
+  auto prefetch = [&](int j0n) {
+    const int nn = min(kTok, n_new - j0n);
+    TileWalk w(D);
+#pragma unroll
+    for (int u = 0; u < kPF; ++u, w.next())
+      if (w.c < nn) {
+        const T* pr = proj + (int64_t)(t0 + j0n + w.c) * proj_stride + h * D;
+        pq[u] = pr[q_off + w.d];
+        pk[u] = pr[k_off + w.d];
+      }
+    TileWalk wv(ncol);
+#pragma unroll
+    for (int u = 0; u < kPFG; ++u, wv.next())
+      if (wv.c < nn) pv[u] = proj[(int64_t)(t0 + j0n + wv.c) * proj_stride + v_off + h * Dv + c0 + wv.d];
+  };
+  prefetch(0);
+  gates(0, sg);
   __syncthreads();
+  if (walker_warp && lane == 0) walk(0, sg);
   int stage = 0;
   for (int j0 = 0; j0 < n_new; j0 += kTok, ++stage) {
     const int n = min(kTok, n_new - j0);
-    for (int i = tid; i < n * D; i += blockDim.x) {
-      const int c = i / D, d = i - c * D;
-      const T* pr = proj + (int64_t)(t0 + j0 + c) * proj_stride + h * D;
-      sq[c * ROW + L::at(d)] = to_f<T>(pr[q_off + d]) * q_scale;
-      sk[c * ROW + L::at(d)] = to_f<T>(pr[k_off + d]);
+    float* cur = sg + (stage & 1) * kTokMax * 4;
+    float* nxt = sg + ((stage + 1) & 1) * kTokMax * 4;
+    {
+      TileWalk w(D);
+#pragma unroll
+      for (int u = 0; u < kPF; ++u, w.next())
+        if (w.c < n) {
+          sq[w.c * ROW + L::at(w.d)] = to_f<T>(pq[u]) * q_scale;
+          sk[w.c * ROW + L::at(w.d)] = to_f<T>(pk[u]);
+        }
+      for (; w.c < n; w.next()) {
+        const T* pr = proj + (int64_t)(t0 + j0 + w.c) * proj_stride + h * D;
+        sq[w.c * ROW + L::at(w.d)] = to_f<T>(pr[q_off + w.d]) * q_scale;
+        sk[w.c * ROW + L::at(w.d)] = to_f<T>(pr[k_off + w.d]);
+      }
+      TileWalk wv(ncol);
+#pragma unroll
+      for (int u = 0; u < kPFG; ++u, wv.next())
+        if (wv.c < n) sv[wv.c * CW + wv.d] = to_f<T>(pv[u]);
+      for (; wv.c < n; wv.next())
+        sv[wv.c * CW + wv.d] = to_f<T>(proj[(int64_t)(t0 + j0 + wv.c) * proj_stride + v_off + h * Dv + c0 + wv.d]);
     }
-    for (int i = tid; i < n * ncol; i += blockDim.x) {
-      const int c = i / ncol, d = i - c * ncol;
-      sv[c * CW + d] = to_f<T>(proj[(int64_t)(t0 + j0 + c) * proj_stride + v_off + h * Dv + c0 + d]);
-    }
-    for (int c = tid; c < n; c += blockDim.x) {   // the capped log gates
-      const T* pr = proj + (int64_t)(t0 + j0 + c) * proj_stride;
-      const float zi = cap * tanhf(to_f<T>(pr[i_off + h]) / cap), zf = cap * tanhf(to_f<T>(pr[f_off + h]) / cap);
-      sc[c * 4 + 0] = zf < -20.f ? zf : -log1pf(expf(-zf));   // logsigmoid
-      sc[c * 4 + 1] = zi;
-    }
+    if (j0 + kTok < n_new) gates(j0 + kTok, nxt);
+    __syncthreads();                    // the stage's rows, this stage's walked gates and the next stage's raw gates are in place
+    if (j0 + kTok < n_new) prefetch(j0 + kTok);
     prefetch_gates<T>(a, pg, h, c0, ncol, t0 + j0, n);
-    __syncthreads();
-    if (warp == 0) {
+    if (walker_warp) {
+      if (lane == 0 && j0 + kTok < n_new) walk(j0 + kTok, nxt);
+    } else {
+      for (int c = warp; c < n; c += workers) {   // k . q of every token: a warp per token
+        float kq = 0.f;
+        for (int d = lane; d < D; d += 32) kq = fmaf(sk[c * ROW + L::at(d)], sq[c * ROW + L::at(d)], kq);
+        kq = warp_sum(kq);
+        if (lane == 0) skq[c * 4] = kq;
+      }
+      // the workers alone meet here (barrier 1): the walker warp is on its way through the next stage's gates
+      asm volatile("bar.sync 1, %0;" ::"r"(wthreads) : "memory");
       for (int c = 0; c < n; ++c) {
-        const float fl = sc[c * 4 + 0], il = sc[c * 4 + 1];
-        const float m_new = fmaxf(fl + mrun, il);
-        const float F = expf(fl + mrun - m_new), I = expf(il - m_new);
-        float nq = 0.f, kq = 0.f;
+        const float vj = valid ? sv[c * CW + j] : (is_n ? 1.f : 0.f);
+        const float F = cur[c * 4 + 0], I = cur[c * 4 + 1];
+        const float* qb = sq + c * ROW + ks * L::SL;
+        const float* kb = sk + c * ROW + ks * L::SL;
+        float2 d[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        const float2 F2 = make_float2(F, F), w2 = make_float2(I * vj, I * vj);
 #pragma unroll
-        for (int e = 0; e < kMaxNormRegs; ++e) {
-          const int d = lane + 32 * e;
-          if (d < D) {
-            const float kv = sk[c * ROW + L::at(d)], qv = sq[c * ROW + L::at(d)];
-            nv[e] = fmaf(F, nv[e], I * kv);
-            nq = fmaf(nv[e], qv, nq);
-            kq = fmaf(kv, qv, kq);
-          }
+        for (int r = 0; r < R; r += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qb + r);
+          const float4 k4 = *reinterpret_cast<const float4*>(kb + r);
+          d[0] = __ffma2_rn(S[r / 2], make_float2(q4.x, q4.y), d[0]);
+          d[1] = __ffma2_rn(S[r / 2 + 1], make_float2(q4.z, q4.w), d[1]);
+          S[r / 2] = __ffma2_rn(make_float2(k4.x, k4.y), w2, __fmul2_rn(F2, S[r / 2]));
+          S[r / 2 + 1] = __ffma2_rn(make_float2(k4.z, k4.w), w2, __fmul2_rn(F2, S[r / 2 + 1]));
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          nq += __shfl_xor_sync(0xffffffffu, nq, o);
-          kq += __shfl_xor_sync(0xffffffffu, kq, o);
-        }
-        mrun = m_new;
-        __syncwarp();
-        if (lane == 0) {
-          sc[c * 4 + 0] = F;
-          sc[c * 4 + 1] = I;
-          sc[c * 4 + 2] = kq;
-          sc[c * 4 + 3] = 1.0f / (fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f);
+        const float ds = slice_sum((d[0].x + d[0].y) + (d[1].x + d[1].y), KS);
+        if (ks == 0) {
+          const float num = fmaf(F, ds, I * skq[c * 4] * vj);
+          if (valid) so[c * CW + j] = num;
+          else if (is_n) sden[c] = num;
         }
       }
     }
     __syncthreads();
-    for (int c = 0; c < n; ++c) {
-      const float vj = valid ? sv[c * CW + j] : 0.f;
-      const float F = sc[c * 4 + 0], I = sc[c * 4 + 1];
-      const float* qb = sq + c * ROW + ks * L::SL;
-      const float* kb = sk + c * ROW + ks * L::SL;
-      float2 d[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      const float2 F2 = make_float2(F, F), w2 = make_float2(I * vj, I * vj);
-#pragma unroll
-      for (int r = 0; r < R; r += 4) {
-        const float4 q4 = *reinterpret_cast<const float4*>(qb + r);
-        const float4 k4 = *reinterpret_cast<const float4*>(kb + r);
-        d[0] = __ffma2_rn(S[r / 2], make_float2(q4.x, q4.y), d[0]);
-        d[1] = __ffma2_rn(S[r / 2 + 1], make_float2(q4.z, q4.w), d[1]);
-        S[r / 2] = __ffma2_rn(make_float2(k4.x, k4.y), w2, __fmul2_rn(F2, S[r / 2]));
-        S[r / 2 + 1] = __ffma2_rn(make_float2(k4.z, k4.w), w2, __fmul2_rn(F2, S[r / 2 + 1]));
-      }
-      const float ds = slice_sum((d[0].x + d[0].y) + (d[1].x + d[1].y), KS);
-      if (ks == 0 && valid) so[c * CW + j] = fmaf(F, ds, I * sc[c * 4 + 2] * vj) * sc[c * 4 + 3];
+    for (int i = tid; i < n * ncol; i += blockDim.x) {
+      const int c = i / ncol, col = i - c * ncol;
+      so[c * CW + col] *= 1.0f / (fmaxf(fabsf(sden[c]), cur[c * 4 + 2]) + 1e-6f);
     }
     __syncthreads();
     gated_unit_norm_rows<T>(a, so, part, sinv, stage, pg, h, c0, ncol, t0 + j0, n);
@@ -849,14 +892,16 @@ __global__ void __launch_bounds__(MAXT) matrix_memory_kernel(const T* __restrict
   }
   if (slot != a.reserved_slot) {
     store_state<R>(S, a, slot, h, c0 + j, valid, ks);
-    if (vt == 0 && warp == 0) {
+    if (vt == 0 && is_n) {
+      float* dst = nvec + ((int64_t)slot * H + h) * D;
 #pragma unroll
-      for (int e = 0; e < kMaxNormRegs; ++e) {
-        const int d = lane + 32 * e;
-        if (d < D) nvec[((int64_t)slot * H + h) * D + d] = nv[e];
+      for (int r = 0; r < R; r += 2) {
+        const int i = ks * R + r;
+        if (i < D) dst[i] = S[r / 2].x;
+        if (i + 1 < D) dst[i + 1] = S[r / 2].y;
       }
-      if (lane == 0) mstate[(int64_t)slot * H + h] = mrun;
     }
+    if (vt == 0 && walker_warp && lane == 0) mstate[(int64_t)slot * H + h] = mrun;
   }
   if (a.VT > 1) cooperative_groups::this_cluster().sync();   // nobody leaves while its sums may still be read
 }
@@ -880,7 +925,8 @@ struct RecurShape {
 // pairs for the SMs - and to as many as it takes (up to 8) for the CTA to fit 1024 threads;
 // R: the shortest register slice in {8, 16, 32} whose CTA fits 512 threads (128 registers a thread), else 1024;
 // KS: the power of two with KS * R >= D.  threads == 0: no layout (D or Dv too large).
-inline RecurShape recur_shape(int D, int Dv, int pairs, int max_new) {
+// `extra`: columns every CTA keeps beside its share of the value columns (the matrix memory's normalizer column).
+inline RecurShape recur_shape(int D, int Dv, int pairs, int max_new, int extra = 0) {
   RecurShape s{};
   const int forced = test_options().recur_layout.load();
   if (forced > 0) {   // tests and measurements: 100 * VT + R, taken when it fits
@@ -890,8 +936,8 @@ inline RecurShape recur_shape(int D, int Dv, int pairs, int max_new) {
       s.CW = Dv / s.VT;
       s.KS = 1;
       while (s.KS * s.R < D) s.KS <<= 1;
-      if (s.KS <= kMaxSlices && s.CW * s.KS <= 1024) {
-        s.threads = cdiv(s.CW * s.KS, 32) * 32;
+      if (s.KS <= kMaxSlices && (s.CW + extra) * s.KS <= 1024 - 32 * extra) {
+        s.threads = cdiv((s.CW + extra) * s.KS, 32) * 32;
         return s;
       }
     }
@@ -906,10 +952,10 @@ inline RecurShape recur_shape(int D, int Dv, int pairs, int max_new) {
     for (int r = 32; r >= 8 && s.R == 0; r >>= 1) {
       int ks = 1;
       while (ks * r < D) ks <<= 1;
-      if (ks <= kMaxSlices && s.CW * ks <= 512) s.R = r, s.KS = ks;
+      if (ks <= kMaxSlices && (s.CW + extra) * ks <= 512 + 32 * extra) s.R = r, s.KS = ks;
     }
     if (s.R != 0) {
-      s.threads = cdiv(s.CW * s.KS, 32) * 32;
+      s.threads = cdiv((s.CW + extra) * s.KS, 32) * 32;
       return s;
     }
     s = RecurShape{};
@@ -927,12 +973,12 @@ inline RecurShape recur_shape(int D, int Dv, int pairs, int max_new) {
       for (int r = 8; r <= 32 && s.R == 0; r <<= 1) {
         int ks = 1;
         while (ks * r < D) ks <<= 1;
-        if (ks <= kMaxSlices && s.CW * ks <= limit) s.R = r, s.KS = ks;
+        if (ks <= kMaxSlices && (s.CW + extra) * ks <= (limit < 1024 ? limit + 32 * extra : limit - 32 * extra)) s.R = r, s.KS = ks;
       }
     if (s.R != 0) break;
     if (s.VT >= 8 || Dv % (2 * s.VT) != 0) return s;   // threads stays 0
   }
-  s.threads = cdiv(s.CW * s.KS, 32) * 32;
+  s.threads = cdiv((s.CW + extra) * s.KS, 32) * 32;
   return s;
 }
 
@@ -1007,7 +1053,9 @@ int launch_matrix_memory(dim3 grid, const RecurShape& sh, cudaStream_t st, const
                          float* mstate, const RecurArgs& a) {
   static std::atomic<uint64_t> attr{0};
   CVLLM_CHECK_CUDA(ensure_max_dyn_smem((const void*)matrix_memory_kernel<T, R, MAXT>, max_recur_smem<R>(2), attr));
-  CVLLM_CHECK_CUDA(launch_clustered(matrix_memory_kernel<T, R, MAXT>, grid, sh.threads, sh.smem(2), st, sh.VT,
+  // + the warp that walks the gates; + the two stages' gate records
+  CVLLM_CHECK_CUDA(launch_clustered(matrix_memory_kernel<T, R, MAXT>, grid, sh.threads + 32,
+                                    sh.smem(2) + sizeof(float) * 8 * kTokMax, st, sh.VT,
                                     static_cast<const T*>(proj), proj_stride, q_off, k_off, v_off, i_off, f_off, cap,
                                     q_scale, nvec, mstate, a));
   CVLLM_CHECK_LAUNCH();
@@ -1155,7 +1203,7 @@ extern "C" int cvllm_matrix_memory(const void* proj, int64_t proj_stride, int q_
   CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
   CVLLM_CHECK_SUPPORTED(D <= kMaxKeyDim && Dv <= kMaxValueDim && H <= 65535 && B <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
-  RecurShape sh = recur_shape(D, Dv, H * B, max_new);
+  RecurShape sh = recur_shape(D, Dv, H * B, max_new, 1);   // one more column per CTA: the normalizer
   sh.pick_tok(max_new, 2);
   CVLLM_CHECK_SUPPORTED(sh.threads > 0 && sh.threads <= 1024 && (int64_t)H * sh.VT <= 2147483647);
   RecurArgs a{{cu_seqlens_q, seq_start, positions, batch_mapping}, state, proj, proj_stride, gate_off, norm_w,
@@ -1164,7 +1212,20 @@ extern "C" int cvllm_matrix_memory(const void* proj, int64_t proj_stride, int q_
 #define CVLLM_MMEM(T, RR, MT)                                                                                       \
   launch_matrix_memory<T, RR, MT>(grid, sh, st, proj, proj_stride, q_off, k_off, v_off, i_off, f_off, cap, q_scale, \
                                   nvec, mstate, a)
-  if (dtype == CVLLM_BF16) { CVLLM_RECUR_BY_R(CVLLM_MMEM, __nv_bfloat16) }
-  CVLLM_RECUR_BY_R(CVLLM_MMEM, float)
+  RecurShape sel = sh;      // the launch bound counts the walking warp
+  sel.threads += 32;
+#define CVLLM_MMEM_BY_T(T, RR) \
+  return sel.threads <= 512 ? CVLLM_MMEM(T, RR, 512) : sel.threads <= 640 ? CVLLM_MMEM(T, RR, 640) : CVLLM_MMEM(T, RR, 1024)
+  // CTAs of up to 640 threads (512 of columns, the normalizer's slices, the walking warp) keep 96 registers a thread
+#define CVLLM_MMEM_BY_R(T)                 \
+  switch (sel.R) {                         \
+    case 8: CVLLM_MMEM_BY_T(T, 8);         \
+    case 16: CVLLM_MMEM_BY_T(T, 16);       \
+    default: CVLLM_MMEM_BY_T(T, 32);       \
+  }
+  if (dtype == CVLLM_BF16) { CVLLM_MMEM_BY_R(__nv_bfloat16) }
+  CVLLM_MMEM_BY_R(float)
+#undef CVLLM_MMEM_BY_R
+#undef CVLLM_MMEM_BY_T
 #undef CVLLM_MMEM
 }

@@ -480,14 +480,16 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __re
 // Selective scan with a decay per (channel, state channel) and a step size per channel:
 //     dt_t[c] = softplus(dt_raw_t[c] + dt_bias[c])      S_t[c, n] = exp(dt_t[c] A[c, n]) S_(t-1)[c, n] + dt_t[c] x_t[c] B_t[n]
 //     y_t[c]  = sum_n S_t[c, n] C_t[n] + D[c] x_t[c]     out_t[c] = y_t[c] silu(z_t[c])
-// with A = -exp(A_log) [channels, N].  grid (channel tiles, B), CT * NS threads: thread (pl, s) keeps the kSelNPT state
-// channels s * kSelNPT .. of channel c0 + pl in registers over the portion's tokens (NS a power of two,
-// NS * kSelNPT >= N); a token's B and C rows, and the tile's step sizes and inputs, are staged kSelTokens tokens at a
-// time.  x, dt_raw, the B | C columns and z are stored projections (model type); the rest is fp32.
-constexpr int kSelTokens = 16;
-constexpr int kSelNPT = 8;
+// with A = -exp(A_log) [channels, N].  grid (channel tiles, B), CT * NS threads: thread (pl, s) keeps the NPT state
+// channels s * NPT .. of channel c0 + pl in registers over the portion's tokens (NS a power of two, NS * NPT >= N);
+// a token's B and C rows, and the tile's step sizes and inputs, are staged kSelTokens tokens at a time.  The work has
+// channels * N independent recurrences and nothing else to run side by side, so NPT is chosen by the host as small as
+// it takes to fill the SMs with threads (one state channel per thread for a single portion of a few thousand channels);
+// the sum over n is NS lanes' shuffles.  x, dt_raw, the B | C columns and z are stored projections (model type); the
+// rest is fp32.
+constexpr int kSelTokens = 32;
 
-template <typename T>
+template <typename T, int NPT>
 __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict__ x, int64_t x_stride,
                                                              const T* __restrict__ dt_raw, int64_t dt_stride,
                                                              const float* __restrict__ dt_bias,
@@ -498,7 +500,7 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
                                                              StepGeom g, T* __restrict__ out, int64_t o_stride,
                                                              int inner, int N, int NS, int CT, int reserved_slot) {
   extern __shared__ __align__(16) float sm[];
-  const int NSP = NS * kSelNPT;
+  const int NSP = NS * NPT;
   float* sB = sm;                              // [kSelTokens][NSP]
   float* sC = sB + kSelTokens * NSP;           // [kSelTokens][NSP]
   float* sdt = sC + kSelTokens * NSP;          // [kSelTokens][CT]
@@ -519,12 +521,12 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
     }
     return;
   }
-  float S[kSelNPT], A[kSelNPT];
-  float* srow = state + ((int64_t)slot * inner + ch) * N + s * kSelNPT;
+  float S[NPT], A[NPT];
+  float* srow = state + ((int64_t)slot * inner + ch) * N + s * NPT;
 #pragma unroll
-  for (int e = 0; e < kSelNPT; ++e) {
-    const bool in = live && s * kSelNPT + e < N;
-    A[e] = in ? -expf(A_log[(int64_t)ch * N + s * kSelNPT + e]) : 0.f;
+  for (int e = 0; e < NPT; ++e) {
+    const bool in = live && s * NPT + e < N;
+    A[e] = in ? -expf(A_log[(int64_t)ch * N + s * NPT + e]) : 0.f;
     S[e] = (in && start > 0) ? srow[e] : 0.f;
   }
   const float dsk = live ? Dp[ch] : 0.f;
@@ -547,11 +549,11 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
     for (int j = 0; j < n; ++j) {
       const float dt = sdt[j * CT + pl], xv = sx[j * CT + pl];
       const float dx = dt * xv;
-      const float* Bj = sB + j * NSP + s * kSelNPT;
-      const float* Cj = sC + j * NSP + s * kSelNPT;
+      const float* Bj = sB + j * NSP + s * NPT;
+      const float* Cj = sC + j * NSP + s * NPT;
       float acc = 0.f;
 #pragma unroll
-      for (int e = 0; e < kSelNPT; ++e) {
+      for (int e = 0; e < NPT; ++e) {
         S[e] = fmaf(expf(dt * A[e]), S[e], dx * Bj[e]);
         acc = fmaf(S[e], Cj[e], acc);
       }
@@ -571,8 +573,8 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
     __syncthreads();
   }
 #pragma unroll
-  for (int e = 0; e < kSelNPT; ++e)
-    if (live && s * kSelNPT + e < N) srow[e] = S[e];
+  for (int e = 0; e < NPT; ++e)
+    if (live && s * NPT + e < N) srow[e] = S[e];
 }
 
 // state channels per thread: 8 (twice the threads, for the latencies of a sequential recurrence) up to N = 256, else 16
@@ -808,29 +810,44 @@ extern "C" int cvllm_selective_scan(const void* x, int64_t x_stride, const void*
   CVLLM_CHECK_ARG(x && dt_raw && dt_bias && bc && A_log && D && z && state && batch_mapping && out &&
                   ssm_dtype_ok(dtype));
   CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
+  // state channels per thread: 8 while that fills the SMs with threads, halved down to 1 otherwise (a portion of a few
+  // thousand channels has nothing but its channels x N recurrences to run side by side); N <= 32 * NPT
+  int npt = 8;
+  while (npt > 1 && N <= 32 * (npt / 2) && (int64_t)B * inner * cdiv(N, npt) < (int64_t)sm_count() * 1536) npt >>= 1;
+  while (npt < 8 && N > 32 * npt) npt <<= 1;
   int NS = 1;
-  while (NS * kSelNPT < N) NS <<= 1;
+  while (NS * npt < N) NS <<= 1;
   CVLLM_CHECK_SUPPORTED(NS <= 32 && B <= 65535);
-  // channels per CTA: 256 threads while that still gives two CTAs per SM, down to 64 threads
-  int threads = 256;
-  while (threads > 64 && threads / NS > 1 && (int64_t)B * cdiv(inner, threads / NS) < 2 * (int64_t)sm_count()) threads >>= 1;
-  if (threads < NS) threads = NS;
+  // up to 256 threads, at most 64 channels a CTA (their staged step sizes, inputs and outputs bound the shared memory)
+  int threads = 64 * NS < 256 ? 64 * NS : 256;
   if (threads < 32) threads = 32;
   const int CT = threads / NS;
   auto st = static_cast<cudaStream_t>(stream);
   const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
   const dim3 grid(cdiv(inner, CT), B);
-  const size_t smem = sizeof(float) * (size_t)kSelTokens * (2 * NS * kSelNPT + 3 * CT);
-  if (dtype == CVLLM_BF16)
-    selective_scan_kernel<__nv_bfloat16><<<grid, threads, smem, st>>>(
-        static_cast<const __nv_bfloat16*>(x), x_stride, static_cast<const __nv_bfloat16*>(dt_raw), dt_stride, dt_bias,
-        static_cast<const __nv_bfloat16*>(bc), bc_stride, b_off, c_off, A_log, D, static_cast<const __nv_bfloat16*>(z),
-        z_stride, z_off, state, g, static_cast<__nv_bfloat16*>(out), out_stride, inner, N, NS, CT, reserved_slot);
-  else
-    selective_scan_kernel<float><<<grid, threads, smem, st>>>(
-        static_cast<const float*>(x), x_stride, static_cast<const float*>(dt_raw), dt_stride, dt_bias,
-        static_cast<const float*>(bc), bc_stride, b_off, c_off, A_log, D, static_cast<const float*>(z), z_stride,
-        z_off, state, g, static_cast<float*>(out), out_stride, inner, N, NS, CT, reserved_slot);
+  const size_t smem = sizeof(float) * (size_t)kSelTokens * (2 * NS * npt + 3 * CT);
+  static std::atomic<uint64_t> sel_mask[8];   // per kernel instance: [type][log2 NPT]
+#define CVLLM_SEL(T, NPT)                                                                                            \
+  do {                                                                                                               \
+    if (smem > 48 * 1024)                                                                                            \
+      CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(selective_scan_kernel<T, NPT>), 128 * 1024, \
+                                           sel_mask[(sizeof(T) == 2 ? 4 : 0) + (NPT == 1 ? 0 : NPT == 2 ? 1 : NPT == 4 ? 2 : 3)])); \
+    selective_scan_kernel<T, NPT><<<grid, threads, smem, st>>>(                                                      \
+        static_cast<const T*>(x), x_stride, static_cast<const T*>(dt_raw), dt_stride, dt_bias,                       \
+        static_cast<const T*>(bc), bc_stride, b_off, c_off, A_log, D, static_cast<const T*>(z), z_stride, z_off,     \
+        state, g, static_cast<T*>(out), out_stride, inner, N, NS, CT, reserved_slot);                                \
+  } while (0)
+#define CVLLM_SEL_BY_NPT(T)                                                                                          \
+  do {                                                                                                               \
+    if (npt == 1) CVLLM_SEL(T, 1);                                                                                   \
+    else if (npt == 2) CVLLM_SEL(T, 2);                                                                              \
+    else if (npt == 4) CVLLM_SEL(T, 4);                                                                              \
+    else CVLLM_SEL(T, 8);                                                                                            \
+  } while (0)
+  if (dtype == CVLLM_BF16) CVLLM_SEL_BY_NPT(__nv_bfloat16);
+  else CVLLM_SEL_BY_NPT(float);
+#undef CVLLM_SEL_BY_NPT
+#undef CVLLM_SEL
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
 }
