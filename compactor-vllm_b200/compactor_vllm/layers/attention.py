@@ -146,6 +146,8 @@ def distance_buckets(rows: int, far: int, length: int) -> list:
     for n in range(length):
         if n < half or half == 0:
             out.append(min(n, rows - 1))
+        elif far <= half:           # no room for logarithmic buckets: everything from `half` on shares the last row
+            out.append(rows - 1)
         else:
             out.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
     return out
@@ -211,7 +213,7 @@ class BiasedChunkAttention(nn.Module):
         if rel is not None:
             self.rel = nn.Parameter(rel.detach().to(device=self.rel.device, dtype=torch.float32).contiguous())
         rows = self.rel.shape[0]
-        length = self.bias_far + 1
+        length = max(self.bias_far, rows // 2) + 1
         if self.window > 0:
             length = min(length, self.window)
         idx = torch.tensor(distance_buckets(rows, self.bias_far, max(length, 1)), dtype=torch.long, device=self.rel.device)
