@@ -443,14 +443,16 @@ int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64_t o_stride
  * largest choices are taken (ties: the lower index).  idx int32 [T, top], wts fp32 [T, top] = the plain s of the
  * chosen outputs, not renormalised.  E <= 2048, E % groups == 0, keep * E / groups >= top.
  * mode 1 (groups 1, no correction, top <= 32): the `top` largest LOGITS are taken and wts is the softmax over the
- * chosen logits alone. */
+ * chosen logits alone.  mode 2 (same limits): the `top` largest sigmoid(logit) are taken - the same choice - and wts
+ * is each chosen output's own sigmoid(logit), not renormalised. */
 int cvllm_moe_route(const float* logits, int64_t l_stride, const float* correction, int T, int E, int top,
                     int groups, int keep, int mode, int32_t* idx, float* wts, cvllm_stream_t stream);
 
 /* out[t, :] = sum_r wts[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :]) + s_t * shared[t, :]
  * in fp32.  y holds one row per (token, choice) pair with a real expert, at the row pos gives (NULL: the pair's
  * own index); outputs idx >= n_real are identity experts (their output is the input h).  shared may be NULL.
- * s_t = sigmoid(shared_gate[t * gate_stride]) (one fp32 logit per token), or 1 when shared_gate is NULL. */
+ * s_t = sigmoid(shared_gate[t * gate_stride]) (one fp32 logit per token), or 1 when shared_gate is NULL.
+ * wts NULL: every weight is 1 (experts whose weight went into their input, cvllm_scaled_rows). */
 int cvllm_moe_combine(const void* y, const int32_t* pos, const float* wts, int top, const int32_t* idx, int n_real,
                       const void* h, const void* shared, const float* shared_gate, int64_t gate_stride, float* out,
                       int64_t rows, int width, int dtype, cvllm_stream_t stream);

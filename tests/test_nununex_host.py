@@ -73,6 +73,8 @@ def test_distance_buckets():
         assert got[:half] == list(range(half)) and got[half] == half        # exact below half, the first shared bucket
         assert all(b2 >= b1 for b1, b2 in zip(got, got[1:])) and max(got) == rows - 1
         assert got[far] == rows - 1 and got[-1] == rows - 1
+    # a far end inside the exact rows leaves no room for logarithmic buckets: the last row takes everything beyond
+    assert distance_buckets(8, 3, 10) == [0, 1, 2, 3, 7, 7, 7, 7, 7, 7]
 
 
 # ---- the oracle against second formulations ----------------------------------------------------------------------
