@@ -647,27 +647,40 @@ __global__ void __launch_bounds__(MAXT) general_delta_kernel(const T* __restrict
   int stage = 0;
   for (int j0 = 0; j0 < n_new; j0 += kTok, ++stage) {
     const int n = min(kTok, n_new - j0);
+    {   // the stage's raw rows, all threads: k, r, the removal-rate logits and the decay logits land in their planes
+      TileWalk w(D);
+      for (; w.c < n; w.next()) {
+        const T* pr = proj + (int64_t)(t0 + j0 + w.c) * proj_stride + h * D;
+        const int at = w.c * ROW + L::at(w.d);
+        sk[at] = to_f<T>(pr[k_off + w.d]);
+        sy[at] = to_f<T>(pr[r_off + w.d]);
+        sa[at] = to_f<T>(pr[a_off + w.d]);
+        sw[at] = to_f<T>(wp[(int64_t)(t0 + j0 + w.c) * w_stride + h * D + w.d]);
+      }
+    }
+    for (int i = tid; i < n * ncol; i += blockDim.x) {
+      const int c = i / ncol, d = i - c * ncol;
+      sv[c * CW + d] = to_f<T>(proj[(int64_t)(t0 + j0 + c) * proj_stride + v_off + h * Dv + c0 + d]);
+    }
+    __syncthreads();
     for (int c = warp; c < n; c += warps) {   // a warp per token: unit key, rates, decays, the token's two scalars
-      const T* pr = proj + (int64_t)(t0 + j0 + c) * proj_stride + h * D;
-      const T* wr = wp + (int64_t)(t0 + j0 + c) * w_stride + h * D;
       float kk = 0.f;
       for (int d = lane; d < D; d += 32) {
-        const float kv = to_f<T>(pr[k_off + d]);
+        const float kv = sk[c * ROW + L::at(d)];
         kk += kv * kv;
       }
       kk = warp_sum(kk);
       const float ki = 1.0f / sqrtf(kk + 1e-6f);
       float rau = 0.f, rk = 0.f;
       for (int d = lane; d < D; d += 32) {
-        const float kv = to_f<T>(pr[k_off + d]), rv = to_f<T>(pr[r_off + d]);
-        const float u = kv * ki, au = sigmoid_f(to_f<T>(pr[a_off + d])) * u;
-        const float w = expf(-rate * sigmoid_f(to_f<T>(wr[d]) + w0[h * D + d]));
         const int at = c * ROW + L::at(d);
+        const float kv = sk[at], rv = sy[at];
+        const float u = kv * ki, au = sigmoid_f(sa[at]) * u;
+        const float w = expf(-rate * sigmoid_f(sw[at] + w0[h * D + d]));
         su[at] = u;
         sy[at] = rv * w;
         sw[at] = w;
         sa[at] = au;
-        sk[at] = kv;
         rau = fmaf(rv, au, rau);
         rk = fmaf(rv, kv, rk);
       }
@@ -677,10 +690,6 @@ __global__ void __launch_bounds__(MAXT) general_delta_kernel(const T* __restrict
         sc[c * 4 + 0] = rau;
         sc[c * 4 + 1] = rk;
       }
-    }
-    for (int i = tid; i < n * ncol; i += blockDim.x) {
-      const int c = i / ncol, d = i - c * ncol;
-      sv[c * CW + d] = to_f<T>(proj[(int64_t)(t0 + j0 + c) * proj_stride + v_off + h * Dv + c0 + d]);
     }
     prefetch_gates<T>(a, pg, h, c0, ncol, t0 + j0, n);
     __syncthreads();
