@@ -676,7 +676,7 @@ __global__ void __launch_bounds__(MAXT) general_delta_kernel(const T* __restrict
         const int at = c * ROW + L::at(d);
         const float kv = sk[at], rv = sy[at];
         const float u = kv * ki, au = sigmoid_f(sa[at]) * u;
-        const float w = expf(-rate * sigmoid_f(sw[at] + w0[h * D + d]));
+        const float w = exp_1ulp(-rate * sigmoid_f(sw[at] + w0[h * D + d]));   // multiplies the state token after token
         su[at] = u;
         sy[at] = rv * w;
         sw[at] = w;
@@ -800,8 +800,8 @@ __global__ void __launch_bounds__(MAXT) matrix_memory_kernel(const T* __restrict
     for (int c = 0; c < nn; ++c) {
       const float fl = dst[c * 4 + 0], il = dst[c * 4 + 1];
       const float m_new = fmaxf(fl + mrun, il);
-      dst[c * 4 + 0] = expf(fl + mrun - m_new);
-      dst[c * 4 + 1] = expf(il - m_new);
+      dst[c * 4 + 0] = exp_1ulp(fl + mrun - m_new);     // the state's factor, token after token
+      dst[c * 4 + 1] = exp_1ulp(il - m_new);
       dst[c * 4 + 2] = expf(-m_new);
       mrun = m_new;
     }

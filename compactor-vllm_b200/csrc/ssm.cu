@@ -554,7 +554,7 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
       float acc = 0.f;
 #pragma unroll
       for (int e = 0; e < NPT; ++e) {
-        S[e] = fmaf(expf(dt * A[e]), S[e], dx * Bj[e]);
+        S[e] = fmaf(exp_1ulp(dt * A[e]), S[e], dx * Bj[e]);
         acc = fmaf(S[e], Cj[e], acc);
       }
 #pragma unroll
